@@ -1,0 +1,463 @@
+"""Tiled float11 codec: torch-facing wrappers over the sm_100a kernels.
+
+Mirrors the interface of the reference's ``compress_tiled_kv.py`` (``compress_tiled_tensor``,
+``TiledCompressedTensor``, ``materialize_tiled_state``) and adds the batched forms the cache
+uses: one launch packs every 128-token block of a prefill (``pack_blocks``), one launch
+unpacks any list of segments (``unpack_segments``).
+
+All tensors are CUDA tensors; kernels run on ``torch.cuda.current_stream``.  There is no CPU
+path: on a CPU tensor, or without the built library, these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence
+
+import torch
+
+from . import _lib
+
+_SUPPORTED_TILE_NBITS = (1, 2, 3, 4)
+_DEFAULT_TILE_NBITS = 3
+
+
+# --------------------------------------------------------------------------------------
+# per-device scratch
+# --------------------------------------------------------------------------------------
+
+class _DeviceScratch:
+    """Pack scratch and the device status word of one GPU (grown on demand, reused)."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.workspace = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+
+    def workspace_for(self, n_tiles: int, tile_elems: int) -> torch.Tensor:
+        need = int(_lib.lib().adacode_pack_workspace_bytes(n_tiles, tile_elems))
+        if self.workspace.numel() < need:
+            # the library wants a zero-filled scratch and leaves it reusable
+            self.workspace = torch.zeros(int(need * 1.25) + 256, dtype=torch.uint8, device=self.device)
+        return self.workspace
+
+
+_scratch: dict[torch.device, _DeviceScratch] = {}
+
+
+def _scratch_for(device: torch.device) -> _DeviceScratch:
+    device = torch.device(device)
+    if device.type != 'cuda':
+        raise _lib.AdacodeError(f'float11 kernels need a CUDA tensor, got device {device} (there is no CPU path)')
+    if device.index is None:
+        device = torch.device('cuda', torch.cuda.current_device())
+    s = _scratch.get(device)
+    if s is None:
+        s = _scratch[device] = _DeviceScratch(device)
+    return s
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def check_device_status(device) -> None:
+    """Read the device status word (synchronises) and raise if a kernel flagged a problem."""
+    s = _scratch_for(torch.device(device))
+    word = int(s.status[0].item())
+    if word:
+        s.status.zero_()
+        problems = []
+        if word & _lib.STATUS_ESCAPE_OVERFLOW:
+            problems.append('escape buffer too small during pack')
+        if word & _lib.STATUS_ESCAPE_UNDERRUN:
+            problems.append('escape list shorter than the code plane requires during unpack')
+        raise _lib.AdacodeError('device status: ' + '; '.join(problems))
+
+
+# --------------------------------------------------------------------------------------
+# containers
+# --------------------------------------------------------------------------------------
+
+@dataclass
+class TiledCompressedTensor:
+    """One packed block, field for field the reference's dataclass
+    (compress_tiled_kv.py:238-342)."""
+
+    sign_mass_data: torch.Tensor
+    exp_data: torch.Tensor
+    invalid_exp: torch.Tensor
+    tile_invalid_base: torch.Tensor
+    left: int
+    right: int
+    nbits: int
+    original_shape: tuple
+    seq_tile_size: int
+    head_dim: int
+    tile_head_dim: int
+    tile_num_lanes: int
+    num_sequence_tiles: int
+    num_kv_heads: int
+    device: torch.device
+    layout: str = 'tiled'
+    decode_kind: str = 'tiled_decode'
+    has_outliers: bool = True
+
+    @property
+    def n_elements(self) -> int:
+        n = 1 if self.original_shape else 0
+        for d in self.original_shape:
+            n *= d
+        return n
+
+    def get_memory(self) -> dict:
+        """compress_tiled_kv.py:269-282."""
+        compressed = (self.sign_mass_data.numel() + self.exp_data.numel() + self.invalid_exp.numel()
+                      + self.tile_invalid_base.numel() * self.tile_invalid_base.element_size())
+        original = self.n_elements * 2
+        return {
+            'compressed_memory': compressed,
+            'original_memory': original,
+            'ratio': 0.0 if original == 0 else compressed / original,
+        }
+
+    def export_state(self) -> dict:
+        """compress_tiled_kv.py:284-306."""
+        state = {
+            'layout': self.layout, 'right': self.right, 'nbits': self.nbits, 'left': self.left,
+            'device': self.device, 'original_shape': self.original_shape,
+            'sign_mass_data': self.sign_mass_data, 'exp_data': self.exp_data,
+            'seq_tile_size': self.seq_tile_size, 'head_dim': self.head_dim,
+            'tile_head_dim': self.tile_head_dim, 'tile_num_lanes': self.tile_num_lanes,
+            'num_sequence_tiles': self.num_sequence_tiles, 'num_kv_heads': self.num_kv_heads,
+            'n_elements': self.n_elements, 'has_outliers': self.has_outliers,
+        }
+        if self.has_outliers:
+            state['invalid_exp'] = self.invalid_exp
+            state['tile_invalid_base'] = self.tile_invalid_base
+        return state
+
+    def export_decode_view(self) -> dict:
+        state = self.export_state()
+        state['kind'] = self.decode_kind
+        return state
+
+    def materialize(self) -> torch.Tensor:
+        """compress_tiled_kv.py:313-337."""
+        B, H, S, D = self.original_shape
+        out = torch.empty((B, H, S, D), dtype=torch.bfloat16, device=self.sign_mass_data.device)
+        unpack_segments([self], out)
+        return out
+
+
+@dataclass
+class PackedChunk:
+    """``n_blocks`` consecutive segments produced by one pack launch with one window.
+    Plane tensors are segment-major; ``segment(j)`` gives views shaped like the reference's
+    per-block ``TiledCompressedTensor``."""
+
+    sign_mant: torch.Tensor      # uint8 [n_blocks, B*H*tile_elems]
+    codes: torch.Tensor          # uint8 [n_blocks, B*H*tile_elems*nbits/8]
+    escapes: torch.Tensor        # uint8 [n_escapes]
+    tile_base: torch.Tensor      # int32 [n_blocks, B*H]
+    seg_offsets: list            # host ints, n_blocks + 1
+    seg_offsets_dev: torch.Tensor  # the same, int64 on the device
+    left: int
+    right: int
+    nbits: int
+    batch: int
+    heads: int
+    seq_tile: int
+    head_dim: int
+    _segments: dict = field(default_factory=dict, repr=False)
+
+    @property
+    def n_blocks(self) -> int:
+        return int(self.sign_mant.shape[0])
+
+    @property
+    def n_escapes(self) -> int:
+        return int(self.seg_offsets[-1])
+
+    def segment(self, j: int) -> TiledCompressedTensor:
+        seg = self._segments.get(j)
+        if seg is None:
+            lo, hi = int(self.seg_offsets[j]), int(self.seg_offsets[j + 1])
+            seg = TiledCompressedTensor(
+                sign_mass_data=self.sign_mant[j], exp_data=self.codes[j], invalid_exp=self.escapes[lo:hi],
+                tile_invalid_base=self.tile_base[j], left=self.left, right=self.right, nbits=self.nbits,
+                original_shape=(self.batch, self.heads, self.seq_tile, self.head_dim),
+                seq_tile_size=self.seq_tile, head_dim=self.head_dim, tile_head_dim=self.head_dim,
+                tile_num_lanes=self.head_dim // 8, num_sequence_tiles=1, num_kv_heads=self.heads,
+                device=self.sign_mant.device)
+            self._segments[j] = seg
+        return seg
+
+    def segments(self) -> list:
+        return [self.segment(j) for j in range(self.n_blocks)]
+
+
+# --------------------------------------------------------------------------------------
+# kernels
+# --------------------------------------------------------------------------------------
+
+def _check_src(x: torch.Tensor) -> torch.Tensor:
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    if x.dim() != 4:
+        raise ValueError(f'Expected 4D [batch, kv_heads, seq, head_dim] tensor, got {tuple(x.shape)}')
+    if x.shape[-1] % 8 != 0:
+        raise ValueError(f'Tiled compressed path requires head_dim % 8 == 0, got {x.shape[-1]}')
+    sb, sh, ss, sd = x.stride()
+    if x.numel() and (sd != 1 or (sb | sh | ss) % 8 != 0 or x.data_ptr() % 16 != 0):
+        x = x.contiguous()
+    return x
+
+
+def pack_blocks(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, need_hist: bool = False,
+                hist_out: Optional[torch.Tensor] = None, escape_capacity: Optional[int] = None):
+    """Pack ``x`` [B, H, n_blocks*seq_tile, D] (bf16, any B/H/S strides) into ``n_blocks`` segments
+    with the window ``(right - 2**nbits + 1, right]`` in one launch.
+
+    Returns ``(PackedChunk, hist)``; ``hist`` is an int32[256] device tensor of all exponents when
+    ``need_hist`` (``hist_out`` is added to instead when given).  One small device-to-host read
+    (segment escape totals and the status word) ends the call.
+    """
+    if nbits not in _SUPPORTED_TILE_NBITS:
+        raise ValueError(f'Tiled compressed path supports nbits in {_SUPPORTED_TILE_NBITS}, got {nbits}')
+    x = _check_src(x)
+    B, H, S, D = x.shape
+    if seq_tile <= 0:
+        raise ValueError('seq_tile_size must be positive')
+    if S % seq_tile != 0:
+        raise ValueError(f'sequence length {S} is not a multiple of seq_tile_size {seq_tile}')
+    n_blocks = S // seq_tile
+    dev = x.device
+    sc = _scratch_for(dev)
+    tile_elems = seq_tile * D
+    n_tiles = B * H * n_blocks
+    n = n_tiles * tile_elems
+    L = _lib.lib()
+
+    sign_mant = torch.empty((n_blocks, B * H * tile_elems), dtype=torch.uint8, device=dev)
+    codes = torch.empty((n_blocks, B * H * tile_elems * nbits // 8), dtype=torch.uint8, device=dev)
+    tile_base = torch.empty((n_blocks, B * H), dtype=torch.int32, device=dev)
+    # [segment offsets (n_blocks+1) | status word] in one int64 buffer -> one D2H read
+    meta = torch.zeros(n_blocks + 2, dtype=torch.int64, device=dev)
+    hist = None
+    if need_hist:
+        hist = hist_out if hist_out is not None else torch.zeros(256, dtype=torch.int32, device=dev)
+    cap = int(escape_capacity) if escape_capacity is not None else max(4096, n // 16)
+    cap = min(cap, max(n, 1))
+    ws = sc.workspace_for(n_tiles, tile_elems)
+    status_ptr = meta.data_ptr() + 8 * (n_blocks + 1)
+    sb, sh, ss, _ = x.stride()
+
+    def launch(capacity: int, hist_t):
+        esc = torch.empty(capacity, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            rc = L.adacode_pack_tiles(
+                x.data_ptr(), sb, sh, ss, B, H, n_blocks, seq_tile, D, int(right), int(nbits),
+                sign_mant.data_ptr(), codes.data_ptr(), esc.data_ptr(), capacity, tile_base.data_ptr(),
+                meta.data_ptr(), 0 if hist_t is None else hist_t.data_ptr(), ws.data_ptr(), ws.numel(),
+                status_ptr, _stream_ptr(dev))
+        _lib.check(rc, 'adacode_pack_tiles')
+        return esc
+
+    escapes = launch(cap, hist)
+    host = meta.cpu()
+    offsets = [int(v) for v in host[: n_blocks + 1].tolist()]
+    total = offsets[-1]
+    status = int(host[n_blocks + 1].item()) & 0xFFFFFFFF
+    if total > cap or (status & _lib.STATUS_ESCAPE_OVERFLOW):
+        meta.zero_()
+        escapes = launch(total, None)   # histogram already complete from the first pass
+        host = meta.cpu()
+        if int(host[n_blocks + 1].item()) & 0xFFFFFFFF:
+            raise _lib.AdacodeError('adacode_pack_tiles: escape overflow after re-run with exact capacity')
+    if escapes.numel() > 2 * total + 65536:
+        escapes = escapes[:total].clone()
+    else:
+        escapes = escapes[:total]
+    chunk = PackedChunk(sign_mant, codes, escapes, tile_base, offsets, meta[: n_blocks + 1], int(right) - 2 ** int(nbits) + 1,
+                        int(right), int(nbits), B, H, seq_tile, D)
+    return chunk, hist
+
+
+def unpack_chunk(chunk: PackedChunk, dst: torch.Tensor, seq_offset: int = 0) -> None:
+    """Unpack every segment of ``chunk`` into ``dst[:, :, seq_offset : seq_offset + n_blocks*seq_tile]``."""
+    B, H, T, D = chunk.batch, chunk.heads, chunk.seq_tile, chunk.head_dim
+    _check_dst(dst, B, H, D, seq_offset + chunk.n_blocks * T)
+    dev = dst.device
+    sc = _scratch_for(dev)
+    view = dst[:, :, seq_offset:]
+    db, dh, ds, _ = dst.stride()
+    seg_off = chunk.seg_offsets_dev
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_unpack_tiles(
+            chunk.sign_mant.data_ptr(), chunk.codes.data_ptr(), chunk.escapes.data_ptr(), chunk.escapes.numel(),
+            chunk.tile_base.data_ptr(), seg_off.data_ptr(), B, H, chunk.n_blocks, T, D,
+            chunk.left, chunk.nbits, view.data_ptr(), db, dh, ds, sc.status.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, 'adacode_unpack_tiles')
+
+
+def _check_dst(dst: torch.Tensor, B: int, H: int, D: int, min_seq: int) -> None:
+    if dst.dtype != torch.bfloat16 or dst.dim() != 4:
+        raise ValueError(f'dst must be a 4D bf16 tensor, got {dst.dtype} {tuple(dst.shape)}')
+    if dst.shape[0] != B or dst.shape[1] != H or dst.shape[3] != D or dst.shape[2] < min_seq:
+        raise ValueError(f'dst shape {tuple(dst.shape)} cannot hold [{B}, {H}, {min_seq}, {D}]')
+    if dst.stride(3) != 1:
+        raise ValueError('dst must have unit stride along head_dim')
+
+
+def build_segment_table(segments: Sequence[TiledCompressedTensor], seq_offsets: Optional[Sequence[int]] = None,
+                        device=None) -> torch.Tensor:
+    """Device array of ``adacode_segment`` records (as uint8) for ``unpack_segments``.
+    ``seq_offsets[i]`` is segment i's first token in the destination; the default stacks the
+    segments one after the other."""
+    n = len(segments)
+    table = (_lib.Segment * max(n, 1))()
+    run = 0
+    for i, seg in enumerate(segments):
+        off = run if seq_offsets is None else int(seq_offsets[i])
+        e = table[i]
+        e.sign_mant = seg.sign_mass_data.data_ptr()
+        e.codes = seg.exp_data.data_ptr()
+        e.escapes = seg.invalid_exp.data_ptr() if seg.invalid_exp.numel() else 0
+        e.tile_base = seg.tile_invalid_base.data_ptr()
+        e.escapes_len = seg.invalid_exp.numel()
+        e.dst_seq_offset = off
+        e.left = int(seg.left)
+        e.nbits = int(seg.nbits)
+        run = off + int(seg.original_shape[-2])
+    raw = bytes(table)[: n * ctypes.sizeof(_lib.Segment)]
+    host = torch.frombuffer(bytearray(raw), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
+    if device is None:
+        device = segments[0].sign_mass_data.device
+    return host.to(device, non_blocking=False)
+
+
+def unpack_segments(segments: Sequence[TiledCompressedTensor], dst: torch.Tensor,
+                    seq_offsets: Optional[Sequence[int]] = None, table: Optional[torch.Tensor] = None) -> None:
+    """Unpack a list of segments (any mix of windows and code lengths) into ``dst`` [B, H, S, D]
+    with one launch.  Replaces the reference's per-segment decode + ``torch.cat``
+    (float_cache_utils.py:1257-1264)."""
+    if not segments:
+        return
+    first = segments[0]
+    B, H, T, D = first.original_shape
+    for seg in segments:
+        if tuple(seg.original_shape) != (B, H, T, D):
+            raise ValueError('all segments of one call must share [batch, kv_heads, seq_tile, head_dim]')
+    _check_dst(dst, B, H, D, 0)
+    dev = dst.device
+    sc = _scratch_for(dev)
+    if table is None:
+        table = build_segment_table(segments, seq_offsets, dev)
+    db, dh, ds, _ = dst.stride()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_unpack_segments(table.data_ptr(), len(segments), B, H, T, D, dst.data_ptr(),
+                                                db, dh, ds, sc.status.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, 'adacode_unpack_segments')
+
+
+def exponent_hist(x: torch.Tensor, hist_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int32[256] device histogram of the exponent field of ``x`` [B, H, S, D]
+    (float_cache_utils.py:883-891)."""
+    x = _check_src(x)
+    dev = x.device
+    _scratch_for(dev)
+    hist = hist_out if hist_out is not None else torch.zeros(256, dtype=torch.int32, device=dev)
+    B, H, S, D = x.shape
+    sb, sh, ss, _ = x.stride()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_hist_bf16(x.data_ptr(), sb, sh, ss, B, H, S, D, hist.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, 'adacode_hist_bf16')
+    return hist
+
+
+def choose_params_device(hists: torch.Tensor) -> torch.Tensor:
+    """(right, nbits) pairs, int32 [n, 2] on the device, for int32 histograms [n, 256];
+    nbits == 0 marks a histogram for which no code length beats 8 bits."""
+    if hists.dtype != torch.int32 or hists.shape[-1] != 256:
+        raise ValueError('expected int32 histograms with 256 bins')
+    h = hists.reshape(-1, 256).contiguous()
+    dev = h.device
+    _scratch_for(dev)
+    out = torch.empty((h.shape[0], 2), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_choose_params(h.data_ptr(), h.shape[0], out.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, 'adacode_choose_params')
+    return out
+
+
+def analysis_best_bits(data_freq, store_index: bool = False):
+    """(right, nbits) for one 256-bin histogram given as a tensor, array or list on the host
+    (float_cache_utils.py:373-398).  Raises IndexError where the reference does."""
+    if store_index:
+        raise NotImplementedError('store_index=True is not used by the float11 cache path')
+    values = data_freq.tolist() if hasattr(data_freq, 'tolist') else list(data_freq)
+    if len(values) != 256:
+        raise ValueError(f'expected 256 bins, got {len(values)}')
+    arr = (ctypes.c_int64 * 256)(*[int(v) for v in values])
+    r, n = ctypes.c_int(0), ctypes.c_int(0)
+    rc = _lib.lib().adacode_choose_params_host(arr, ctypes.byref(r), ctypes.byref(n))
+    if rc == _lib.ERR_NO_CANDIDATE:
+        raise IndexError('list index out of range')
+    _lib.check(rc, 'adacode_choose_params_host')
+    return int(r.value), int(n.value)
+
+
+# --------------------------------------------------------------------------------------
+# reference-shaped entry points
+# --------------------------------------------------------------------------------------
+
+def compress_tiled_tensor(original_data_bfloat16: torch.Tensor, right: int, nbits: int = _DEFAULT_TILE_NBITS,
+                          seq_tile_size: int = 128, tile_head_dim: Optional[int] = None,
+                          need_adjust: bool = False):
+    """Pack exactly one block; same arguments, checks and return value as the reference
+    (compress_tiled_kv.py:591-630)."""
+    if nbits not in _SUPPORTED_TILE_NBITS:
+        raise ValueError(f'Tiled compressed path supports nbits in {_SUPPORTED_TILE_NBITS}, got {nbits}')
+    if original_data_bfloat16.dtype != torch.bfloat16:
+        original_data_bfloat16 = original_data_bfloat16.to(torch.bfloat16)
+    if original_data_bfloat16.dim() != 4:
+        raise ValueError(
+            f'Expected 4D [batch, kv_heads, seq, head_dim] tensor, got {tuple(original_data_bfloat16.shape)}')
+    _, _, seq_len, head_dim = original_data_bfloat16.shape
+    if seq_tile_size <= 0:
+        raise ValueError('seq_tile_size must be positive')
+    if tile_head_dim is None:
+        tile_head_dim = head_dim
+    if tile_head_dim != head_dim:
+        raise ValueError(
+            f'Tiled compressed path currently requires tile_head_dim == head_dim, got {tile_head_dim} vs {head_dim}')
+    if head_dim % 8 != 0:
+        raise ValueError(f'Tiled compressed path requires head_dim % 8 == 0, got {head_dim}')
+    if seq_tile_size != seq_len:
+        raise ValueError(
+            'Tiled compressed path currently requires seq_tile_size == seq_len per compressed block, '
+            f'got seq_tile_size={seq_tile_size}, seq_len={seq_len}')
+    chunk, hist = pack_blocks(original_data_bfloat16, right, nbits, seq_tile_size, need_hist=need_adjust)
+    return chunk.segment(0), hist
+
+
+def tensor_from_state(state: dict) -> TiledCompressedTensor:
+    dev = state['device']
+    return TiledCompressedTensor(
+        sign_mass_data=state['sign_mass_data'], exp_data=state['exp_data'],
+        invalid_exp=state.get('invalid_exp', torch.empty((0,), dtype=torch.uint8, device=dev)),
+        tile_invalid_base=state.get('tile_invalid_base', torch.empty((0,), dtype=torch.int32, device=dev)),
+        left=state['left'], right=state['right'], nbits=state['nbits'],
+        original_shape=tuple(state['original_shape']), seq_tile_size=state['seq_tile_size'],
+        head_dim=state['head_dim'], tile_head_dim=state['tile_head_dim'],
+        tile_num_lanes=state['tile_num_lanes'],
+        num_sequence_tiles=int(state.get('num_sequence_tiles', 1)), num_kv_heads=state['num_kv_heads'],
+        device=dev)
+
+
+def materialize_tiled_state(state: dict) -> torch.Tensor:
+    """Dense bf16 tensor of one exported segment state (compress_tiled_kv.py:754-791)."""
+    if state.get('layout') == 'tiled_open_rows':
+        raise NotImplementedError('open-row tiles are not produced by the segmented_tiled cache path')
+    return tensor_from_state(state).materialize()

@@ -1,0 +1,164 @@
+/*
+ * adacode.h — C ABI of the B200 (sm_100a) float11 KV-cache codec.
+ *
+ * float11 stores a bf16 tensor losslessly as
+ *   - one sign/mantissa byte per element,
+ *   - an n-bit exponent code per element (n in 1..4) against a window
+ *     (left, right], left = right - 2**n + 1, eight codes forming one big-endian
+ *     n-byte word with element 0 in the most significant bits,
+ *   - an escape list holding the raw exponent of every element whose exponent
+ *     is outside the window (code 0), in flat [b][h][s][d] order,
+ *   - per (b,h) tile the inclusive running escape count ("tile base").
+ * A "tile" is seq_tile consecutive tokens of one (batch, kv head): seq_tile*D
+ * elements.  A "segment" is all B*H tiles of one seq_tile-token block.
+ *
+ * Conventions: every function returns 0 (ADACODE_OK) or a negative code, never
+ * throws, never synchronises the device and never allocates device memory
+ * unless stated.  All buffers belong to the caller.  `stream` is a
+ * cudaStream_t passed as void*.  Device-side problems (escape capacity
+ * exceeded, escape list too short) are reported by OR-ing bits into
+ * *status (a device int32 the caller zeroes and reads when it wishes).
+ *
+ * Each entry point names the interface of the reference implementation
+ * (lichangshiwhu/Adacode, paths relative to that project) that it replaces.
+ */
+#ifndef ADACODE_H_
+#define ADACODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADACODE_OK 0
+#define ADACODE_ERR_INVALID_ARG (-1)
+#define ADACODE_ERR_CUDA (-2)
+#define ADACODE_ERR_WORKSPACE (-3)
+#define ADACODE_ERR_NO_CANDIDATE (-4) /* adjuster: nothing beats 8 bits per exponent */
+#define ADACODE_ERR_TOO_LARGE (-5)
+
+/* bits OR-ed into the device status word */
+#define ADACODE_STATUS_ESCAPE_OVERFLOW 1 /* pack: escapes_capacity too small, stream truncated */
+#define ADACODE_STATUS_ESCAPE_UNDERRUN 2 /* unpack: a tile wanted an escape beyond n_escapes */
+
+/* Library version, major*10000 + minor*100 + patch. */
+int adacode_version(void);
+
+/* Text for a return code of this library. */
+const char *adacode_strerror(int code);
+
+/* Last CUDA runtime error string seen by this library on the calling thread
+ * (valid after a call returned ADACODE_ERR_CUDA). */
+const char *adacode_last_cuda_error(void);
+
+/*
+ * Bytes of scratch `adacode_pack_tiles` needs for a call that packs
+ * n_tiles = B*H*n_blocks tiles of tile_elems = seq_tile*D elements.
+ * The scratch must be zero-filled once when it is allocated; the library
+ * leaves it ready for the next call.  Calls sharing one scratch buffer must
+ * be ordered on one stream.
+ */
+size_t adacode_pack_workspace_bytes(int64_t n_tiles, int64_t tile_elems);
+
+/*
+ * Pack n_blocks consecutive seq_tile-token blocks of a bf16 tensor
+ * src[B][H][n_blocks*seq_tile][D] (element strides stride_b/h/s, unit stride
+ * along D) with one window.
+ * Replaces: compress_tiled_tensor / _build_tiled_tensor
+ *   (compress_tiled_kv.py:591-630, :524-588), which run
+ *   CompressorBitMap.compress (compress_bitmap_merge.py:768-822):
+ *   get_exp_mask_count_fused_kernel (:179-208), the boolean-mask gather and
+ *   cumsum of get_invalid_index_values (:210-254) and compress{1,2,3,4}bit_vector
+ *   (:256-420) once per block; and the pure-torch equivalent
+ *   compress_open_tiled_rows + seal_open_tiled_rows (compress_tiled_kv.py:721-751,
+ *   :633-718).
+ *
+ * Outputs are segment-major, i.e. block j owns
+ *   sign_mant [j*B*H*tile_elems, (j+1)*B*H*tile_elems)            (sign_mass_data)
+ *   codes     [j*B*H*tile_elems*nbits/8, ...)                     (exp_data)
+ *   tile_base [j*B*H, (j+1)*B*H)   inclusive, restarting at every block (tile_invalid_base)
+ *   escapes   [seg_escape_offsets[j], seg_escape_offsets[j+1])    (invalid_exp)
+ * seg_escape_offsets has n_blocks+1 int64 entries, entry 0 is 0.
+ * hist256 (nullable) receives += the 256-bin histogram of all exponents.
+ * Requirements: D % 8 == 0, 1 <= nbits <= 4, 16-byte aligned src/sign_mant/codes,
+ * strides multiples of 8, B*H*n_blocks*seq_tile*D < 2**31.
+ */
+int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                       int B, int H, int n_blocks, int seq_tile, int D, int right, int nbits,
+                       uint8_t *sign_mant, uint8_t *codes, uint8_t *escapes, int64_t escapes_capacity,
+                       int32_t *tile_base, int64_t *seg_escape_offsets, int32_t *hist256,
+                       void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
+ * Inverse of adacode_pack_tiles for planes laid out as that call writes them.
+ * Replaces: TiledCompressedTensor.materialize / materialize_tiled_state /
+ *   _decode_tiled_bf16_kernel (compress_tiled_kv.py:313-337, :754-791, :33-93),
+ *   one launch for n_blocks segments instead of one per segment plus torch.cat.
+ * Block j is written to dst[b][h][j*seq_tile + r][d] using the dst element strides.
+ * seg_escape_offsets may be NULL when n_blocks == 1.  escapes_len bounds the reads.
+ */
+int adacode_unpack_tiles(const uint8_t *sign_mant, const uint8_t *codes, const uint8_t *escapes,
+                         int64_t escapes_len, const int32_t *tile_base, const int64_t *seg_escape_offsets,
+                         int B, int H, int n_blocks, int seq_tile, int D, int left, int nbits,
+                         void *dst_bf16, int64_t dstride_b, int64_t dstride_h, int64_t dstride_s,
+                         int32_t *status, void *stream);
+
+/*
+ * One packed segment as the cache stores it; an array of these in DEVICE memory
+ * describes a whole layer (segments may differ in window and code length).
+ */
+typedef struct adacode_segment {
+    const uint8_t *sign_mant; /* B*H*tile_elems bytes */
+    const uint8_t *codes;     /* B*H*tile_elems*nbits/8 bytes */
+    const uint8_t *escapes;   /* escapes_len bytes */
+    const int32_t *tile_base; /* B*H inclusive counts */
+    int64_t escapes_len;
+    int64_t dst_seq_offset;   /* first token of this segment in dst */
+    int32_t left;
+    int32_t nbits;
+} adacode_segment;
+
+/*
+ * Unpack n_segments segments described by a device array in one launch.
+ * Replaces: float11Layer._materialize_prefix_segmented_tiled / _materialize_segments
+ *   (float_cache_utils.py:1245-1264, :940-949): a Python loop of one decode launch
+ *   per segment followed by torch.cat.
+ */
+int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments, int B, int H,
+                            int seq_tile, int D, void *dst_bf16, int64_t dstride_b, int64_t dstride_h,
+                            int64_t dstride_s, int32_t *status, void *stream);
+
+/*
+ * hist256 += 256-bin histogram of the exponent field of src[B][H][S][D].
+ * Replaces: float11Layer._extract_exponent_histogram (float_cache_utils.py:883-891)
+ *   and the histogram half of get_exp_mask_count_fused_kernel
+ *   (compress_bitmap_merge.py:205-208).
+ */
+int adacode_hist_bf16(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                      int B, int H, int S, int D, int32_t *hist256, void *stream);
+
+/*
+ * Code-length adjuster on the device: reads n_hists histograms (int32[256] each)
+ * and writes (right, nbits) int32 pairs; nbits == 0 marks "no candidate".
+ * Replaces: analysis_best_bits / _compute_adjusted_params
+ *   (float_cache_utils.py:373-402), without the histogram .to('cpu') round trip.
+ */
+int adacode_choose_params(const int32_t *hist256_dev, int n_hists, int32_t *right_nbits_dev, void *stream);
+
+/* The same rule on host memory (int64 histogram).  Returns ADACODE_ERR_NO_CANDIDATE
+ * where the reference raises IndexError. */
+int adacode_choose_params_host(const int64_t *hist256, int *right, int *nbits);
+
+/*
+ * Offline calibration rule on host memory: code lengths 1..8 with 2**n coded bins.
+ * Replaces: analysis_best_bits_coo (best_bit_analysis_kv_cache.py:28-59), used by
+ *   export_initial_compress_parameters (:191-204).
+ */
+int adacode_calibrate_host(const int64_t *hist256, int *right, int *nbits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADACODE_H_ */

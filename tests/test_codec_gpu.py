@@ -1,0 +1,179 @@
+"""GPU parity of the pack / unpack / histogram / adjuster kernels, called through the C ABI
+(ctypes), against the CPU oracle on identical seeded inputs.  Bit-exact comparison throughout
+(integer/byte work)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import float11_oracle as O
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _u16(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _check_chunk_against_oracle(chunk, hist, x_cpu, right, nbits, seq_tile):
+    B, H, S, D = x_cpu.shape
+    total_hist = np.zeros(256, np.int64)
+    for j in range(S // seq_tile):
+        blk = x_cpu[:, :, j * seq_tile:(j + 1) * seq_tile, :].contiguous()
+        ref = O.pack_block(blk, right, nbits, need_hist=True)
+        seg = chunk.segment(j)
+        assert np.array_equal(seg.sign_mass_data.cpu().numpy(), ref.sign_mass_data), f'sign/mantissa plane, block {j}'
+        assert np.array_equal(seg.exp_data.cpu().numpy(), ref.exp_data), f'code plane, block {j}'
+        assert np.array_equal(seg.tile_invalid_base.cpu().numpy(), ref.tile_invalid_base), f'tile base, block {j}'
+        assert np.array_equal(seg.invalid_exp.cpu().numpy(), ref.invalid_exp), f'escape stream, block {j}'
+        assert seg.left == ref.left and seg.get_memory()['compressed_memory'] == ref.compressed_bytes()
+        total_hist += ref.hist
+    if hist is not None:
+        assert np.array_equal(hist.cpu().numpy().astype(np.int64), total_hist)
+
+
+@pytest.mark.parametrize('nbits', [1, 2, 3, 4])
+@pytest.mark.parametrize('shape', [(1, 8, 128, 128), (3, 2, 256, 64), (2, 1, 128, 512), (1, 2, 128, 72), (2, 3, 384, 16)])
+def test_pack_matches_oracle_and_round_trips(cuda_device, nbits, shape):
+    from adacode_b200 import codec
+    x_cpu = synth.kv_tensor(shape, seed=7 + nbits, key_offset=True)
+    x = x_cpu.to(cuda_device)
+    right = 129
+    chunk, hist = codec.pack_blocks(x, right, nbits, 128, need_hist=True)
+    _check_chunk_against_oracle(chunk, hist, x_cpu, right, nbits, 128)
+    out = torch.zeros_like(x)
+    codec.unpack_chunk(chunk, out)
+    assert np.array_equal(_u16(out), _u16(x_cpu))
+    out2 = torch.zeros_like(x)
+    codec.unpack_segments(chunk.segments(), out2)
+    assert np.array_equal(_u16(out2), _u16(x_cpu))
+    codec.check_device_status(cuda_device)
+
+
+@pytest.mark.parametrize('nbits,right', [(3, 3), (2, 255), (4, 14), (1, 127), (3, 260)])
+def test_all_bf16_patterns_and_extreme_windows(cuda_device, nbits, right):
+    """Every bf16 pattern (zeros, subnormals, Inf, NaN) with windows that reach below 0 and
+    above 255, where nearly everything escapes (the reference's own fixture uses right=3)."""
+    from adacode_b200 import codec
+    x_cpu = synth.all_bf16_patterns()
+    x = x_cpu.to(cuda_device)
+    chunk, hist = codec.pack_blocks(x, right, nbits, 128, need_hist=True)
+    _check_chunk_against_oracle(chunk, hist, x_cpu, right, nbits, 128)
+    out = torch.zeros_like(x)
+    codec.unpack_chunk(chunk, out)
+    assert np.array_equal(_u16(out), _u16(x_cpu))
+    codec.check_device_status(cuda_device)
+
+
+def test_strided_source_and_destination(cuda_device):
+    """K/V arrive as [B, S, H, D] projections viewed as [B, H, S, D]; the kernels take the strides."""
+    from adacode_b200 import codec
+    base_cpu = synth.kv_tensor((2, 256, 4, 128), seed=3)          # [B, S, H, D]
+    x_cpu = base_cpu.transpose(1, 2)                              # [B, H, S, D] view
+    x = base_cpu.to(cuda_device).transpose(1, 2)
+    assert not x.is_contiguous()
+    chunk, hist = codec.pack_blocks(x, 128, 3, 128, need_hist=True)
+    _check_chunk_against_oracle(chunk, hist, x_cpu.contiguous(), 128, 3, 128)
+    wide = torch.zeros((2, 4, 256 + 40, 128), dtype=torch.bfloat16, device=cuda_device)
+    codec.unpack_chunk(chunk, wide, seq_offset=40)
+    assert np.array_equal(_u16(wide[:, :, 40:]), _u16(x_cpu.contiguous()))
+    assert int(wide[:, :, :40].abs().sum()) == 0
+
+
+def test_mixed_segments_one_launch(cuda_device):
+    from adacode_b200 import codec
+    x_cpu = synth.kv_tensor((2, 4, 384, 128), seed=11)
+    x = x_cpu.to(cuda_device)
+    params = [(129, 3), (131, 4), (127, 2)]
+    segs = []
+    for j, (r, n) in enumerate(params):
+        seg, _ = codec.compress_tiled_tensor(x[:, :, j * 128:(j + 1) * 128], right=r, nbits=n, seq_tile_size=128)
+        ref = O.pack_block(x_cpu[:, :, j * 128:(j + 1) * 128].contiguous(), r, n)
+        assert np.array_equal(seg.invalid_exp.cpu().numpy(), ref.invalid_exp)
+        assert np.array_equal(seg.exp_data.cpu().numpy(), ref.exp_data)
+        segs.append(seg)
+    out = torch.zeros_like(x)
+    codec.unpack_segments(segs, out)
+    assert np.array_equal(_u16(out), _u16(x_cpu))
+    # materialize() of a single segment and of its exported state
+    one = segs[1].materialize()
+    assert np.array_equal(_u16(one), _u16(x_cpu[:, :, 128:256].contiguous()))
+    again = codec.materialize_tiled_state(segs[1].export_state())
+    assert torch.equal(one, again)
+
+
+def test_injected_escapes_linear_checksum(cuda_device):
+    """Config-4-style escapes (0.1 % out of window, 0.01 % zero/subnormal): byte parity on a
+    reduced replica and the size-independent property sum(compressed bytes) == formula."""
+    from adacode_b200 import codec
+    x_cpu = synth.inject_escapes(synth.kv_tensor((4, 8, 512, 128), seed=5), seed=6, left=122, right=129)
+    x = x_cpu.to(cuda_device)
+    chunk, hist = codec.pack_blocks(x, 129, 3, 128, need_hist=True)
+    _check_chunk_against_oracle(chunk, hist, x_cpu, 129, 3, 128)
+    n = x.numel()
+    total = sum(chunk.segment(j).get_memory()['compressed_memory'] for j in range(chunk.n_blocks))
+    assert total == n + n * 3 // 8 + chunk.n_escapes + 4 * 4 * 8 * chunk.n_blocks
+    assert int(hist.sum()) == n
+
+
+def test_escape_capacity_retry(cuda_device):
+    from adacode_b200 import codec
+    x_cpu = synth.all_bf16_patterns()
+    x = x_cpu.to(cuda_device)
+    chunk, _ = codec.pack_blocks(x, 3, 3, 128, escape_capacity=64)     # nearly everything escapes
+    ref = O.pack_block(x_cpu, 3, 3)
+    assert np.array_equal(chunk.segment(0).invalid_exp.cpu().numpy(), ref.invalid_exp)
+    codec.check_device_status(cuda_device)
+
+
+def test_histogram_kernel(cuda_device):
+    from adacode_b200 import codec
+    x_cpu = synth.kv_tensor((2, 3, 77, 64), seed=9, key_offset=True)
+    h = codec.exponent_hist(x_cpu.to(cuda_device))
+    assert np.array_equal(h.cpu().numpy().astype(np.int64), O.exponent_hist(x_cpu))
+    strided = x_cpu.to(cuda_device)[:, :, 5:50]
+    h2 = codec.exponent_hist(strided)
+    assert np.array_equal(h2.cpu().numpy().astype(np.int64), O.exponent_hist(x_cpu[:, :, 5:50].contiguous()))
+
+
+def test_adjuster_device_and_host(cuda_device):
+    from adacode_b200 import codec
+    rng = np.random.default_rng(0)
+    hists = []
+    for i in range(40):
+        h = np.zeros(256, np.int64)
+        centre = int(rng.integers(100, 140))
+        width = int(rng.integers(1, 12))
+        idx = np.clip(np.round(rng.normal(centre, width, 20000)).astype(int), 0, 255)
+        np.add.at(h, idx, 1)
+        if i % 5 == 0:                               # ties and zero-count bins
+            h[centre - 1] = h[centre] = h[centre + 1]
+        hists.append(h)
+    hists.append(np.zeros(256, np.int64))            # nothing seen: no candidate
+    hists.append(np.full(256, 10, np.int64))         # flat: no candidate
+    dev_out = codec.choose_params_device(torch.tensor(np.stack(hists), dtype=torch.int32, device=cuda_device)).cpu().numpy()
+    for h, (r, n) in zip(hists, dev_out):
+        try:
+            exp = O.choose_params(h)
+        except IndexError:
+            assert n == 0
+            with pytest.raises(IndexError):
+                codec.analysis_best_bits(h)
+            continue
+        assert (int(r), int(n)) == exp
+        assert codec.analysis_best_bits(torch.tensor(h)) == exp
+
+
+def test_argument_errors(cuda_device):
+    from adacode_b200 import codec
+    x = torch.zeros((1, 2, 128, 64), dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError):
+        codec.compress_tiled_tensor(x, right=129, nbits=5)
+    with pytest.raises(ValueError):
+        codec.compress_tiled_tensor(x[0], right=129, nbits=3)
+    with pytest.raises(ValueError):
+        codec.compress_tiled_tensor(x[..., :60], right=129, nbits=3)
+    with pytest.raises(ValueError):
+        codec.compress_tiled_tensor(x, right=129, nbits=3, seq_tile_size=64)
+    with pytest.raises(Exception):
+        codec.pack_blocks(x.cpu(), 129, 3)
