@@ -1,0 +1,104 @@
+"""Kernel-level timing of pack and unpack on one GPU, for profiling and tuning.
+
+``python -m adacode_b200.microbench --shape 16,8,8192,128 --nbits 4 --right 131 --iters 5``
+
+Packs a seeded synthetic K tensor [B, H, S, D] (all S/128 blocks in one launch) and unpacks it
+again, timing each kernel with CUDA events on the launching stream, and prints one line per
+kernel with the algorithmic HBM bytes (2 read + 1 + nbits/8 + p written per element for pack,
+the mirror image for unpack, p = escape fraction) divided by the time.  Inputs are larger
+than L2 when the shape is; nothing is copied from or to the host inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _lib, codec
+
+
+def synthetic_keys(shape, seed: int = 0, device='cuda') -> torch.Tensor:
+    """N(0, sigma_c) with sigma_c ~ LogNormal(0, 1), 2 % outlier channels x30 and a per-channel
+    offset ~ N(0, 2); a 2048-token slab is generated once and repeated along batch and sequence."""
+    B, H, S, D = shape
+    g = torch.Generator('cpu').manual_seed(seed)
+    base_s = min(S, 2048)
+    sigma = torch.exp(torch.randn(H, D, generator=g))
+    sigma = torch.where(torch.rand(H, D, generator=g) < 0.02, sigma * 30.0, sigma)
+    x = torch.randn(1, H, base_s, D, generator=g) * sigma[None, :, None, :]
+    x = (x + (2.0 * torch.randn(H, D, generator=g))[None, :, None, :]).to(torch.bfloat16).to(device)
+    reps = (S + base_s - 1) // base_s
+    return x.repeat(B, 1, reps, 1)[:, :, :S].contiguous()
+
+
+def _time(fn, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2] * 1e-3
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--shape', default='16,8,8192,128')
+    ap.add_argument('--nbits', type=int, default=4)
+    ap.add_argument('--right', type=int, default=131)
+    ap.add_argument('--seq-tile', type=int, default=128)
+    ap.add_argument('--iters', type=int, default=5)
+    ap.add_argument('--warmup', type=int, default=2)
+    ap.add_argument('--no-hist', action='store_true')
+    args = ap.parse_args()
+    shape = tuple(int(v) for v in args.shape.split(','))
+    B, H, S, D = shape
+    dev = torch.device('cuda', 0)
+    x = synthetic_keys(shape, device=dev)
+    n = x.numel()
+    T = args.seq_tile
+    n_blocks = S // T
+    chunk, _ = codec.pack_blocks(x, args.right, args.nbits, T, need_hist=True)
+    p = chunk.n_escapes / n
+    out = torch.empty_like(x)
+    L = _lib.lib()
+    sc = codec._scratch_for(dev)
+    ws = sc.workspace_for(B * H * n_blocks, T * D)
+    meta = torch.zeros(n_blocks + 2, dtype=torch.int64, device=dev)
+    esc = torch.empty(max(chunk.n_escapes, 16), dtype=torch.uint8, device=dev)
+    hist = torch.zeros(256, dtype=torch.int32, device=dev)
+    sb, sh, ss, _ = x.stride()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def pack():
+        rc = L.adacode_pack_tiles(x.data_ptr(), sb, sh, ss, B, H, n_blocks, T, D, args.right, args.nbits,
+                                  chunk.sign_mant.data_ptr(), chunk.codes.data_ptr(), esc.data_ptr(), esc.numel(),
+                                  chunk.tile_base.data_ptr(), meta.data_ptr(),
+                                  0 if args.no_hist else hist.data_ptr(), ws.data_ptr(), ws.numel(),
+                                  meta.data_ptr() + 8 * (n_blocks + 1), stream)
+        _lib.check(rc, 'adacode_pack_tiles')
+
+    def unpack():
+        codec.unpack_chunk(chunk, out)
+
+    t_pack = _time(pack, args.iters, args.warmup)
+    t_unpack = _time(unpack, args.iters, args.warmup)
+    assert torch.equal(out.view(torch.int16), x.view(torch.int16)), 'round trip is not bit-exact'
+    alg = n * (3.0 + args.nbits / 8.0 + p)
+    for name, t in (('pack', t_pack), ('unpack', t_unpack)):
+        print(json.dumps({
+            'kernel': name, 'shape': list(shape), 'nbits': args.nbits, 'right': args.right,
+            'escape_fraction': round(p, 5), 'us': round(t * 1e6, 1),
+            'algorithmic_GBps': round(alg / t / 1e9, 1), 'bf16_equiv_GBps': round(2 * n / t / 1e9, 1),
+        }))
+
+
+if __name__ == '__main__':
+    main()

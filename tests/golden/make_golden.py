@@ -1,0 +1,221 @@
+"""Writes the golden fixtures in this directory by running the REFERENCE implementation.
+
+Run only where the reference source tree is available:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference is imported as the package ``kv_compression`` (its modules import each other
+under that name) through a temporary directory holding one symlink.  Nothing here is needed
+at test time: the tests read the JSON files this script wrote.
+
+What is recorded
+  * ``codec_vectors.json``  — SHA-256 digests of the four byte streams the reference's pack
+    produces (its pure-torch path ``compress_open_tiled_rows`` + ``seal_open_tiled_rows`` for
+    batch 1, its Triton kernels run by the Triton interpreter on small batched shapes), the
+    escape counts, and the two known answers of the reference's own validation fixture.
+  * ``adjuster_vectors.json`` — ``analysis_best_bits`` / ``analysis_best_bits_coo`` results for
+    seeded histograms, and ``export_initial_compress_parameters`` on a calibration JSON.
+  * ``state_machine.json`` — for every scenario in ``tests/scenarios.py`` the digest of the
+    reference cache after replaying it.
+
+How the reference is driven for the state-machine scenarios: its ``float_cache_utils`` module
+calls ``compress_tiled_tensor`` and ``materialize_tiled_state`` through module-level names.
+For speed those two names are rebound to the reference's own pure-torch pack (batch 1) or to
+the CPU oracle (batch > 1, after the oracle was checked against the reference's kernels in
+the same run) and to the oracle's unpack (checked against ``_decode_tiled_bf16_kernel`` under
+the interpreter in the same run).  Everything else — the whole state machine — is the
+reference's code, unmodified.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import tempfile
+
+os.environ.setdefault('TRITON_INTERPRET', '1')
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+
+def _import_reference(path: str):
+    tmp = tempfile.mkdtemp(prefix='refpkg_')
+    os.symlink(os.path.abspath(path), os.path.join(tmp, 'kv_compression'))
+    sys.path.insert(0, tmp)
+
+
+def main() -> None:
+    ref_path = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    _import_reference(ref_path)
+    import numpy as np
+    import torch
+    from kv_compression import compress_tiled_kv as ref_codec
+    from kv_compression import float_cache_utils as ref_cache
+    from kv_compression import mla_float_cache_utils as ref_mla
+    from kv_compression import best_bit_analysis_kv_cache as ref_calib
+    from oracle import float11_oracle as O
+    from tests import scenarios, synth
+
+    def digest_tensor(t):
+        return {
+            'n_escapes': int(t.invalid_exp.numel()),
+            'sign_mass_data': scenarios._sha(t.sign_mass_data), 'exp_data': scenarios._sha(t.exp_data),
+            'invalid_exp': scenarios._sha(t.invalid_exp),
+            'tile_invalid_base': scenarios._sha(t.tile_invalid_base.to(torch.int32)),
+            'left': int(t.left), 'compressed_memory': int(t.get_memory()['compressed_memory']),
+        }
+
+    # ---------------------------------------------------------------- codec vectors
+    codec_cases = []
+    for nbits in (1, 2, 3, 4):
+        for seed, shape, right in ((0, (1, 8, 128, 128), 129), (1, (1, 2, 128, 512), 127), (2, (1, 4, 128, 64), 131)):
+            x = synth.kv_tensor(shape, seed=seed, key_offset=True)
+            rows, hist = ref_codec.compress_open_tiled_rows(x, right=right, nbits=nbits, need_adjust=True)
+            sealed = ref_codec.seal_open_tiled_rows(rows)
+            d = digest_tensor(sealed)
+            d.update(path='pure_torch', seed=seed, shape=list(shape), right=right, nbits=nbits,
+                     hist=[int(v) for v in hist.tolist()])
+            codec_cases.append(d)
+            # the oracle agrees (fail here, not later, if it does not)
+            p = O.pack_block(x, right, nbits, need_hist=True)
+            assert scenarios._sha(p.invalid_exp) == d['invalid_exp'] and scenarios._sha(p.exp_data) == d['exp_data']
+        for seed, shape, right in ((3, (3, 2, 128, 16), 128), (4, (2, 2, 128, 32), 3)):
+            x = synth.kv_tensor(shape, seed=seed)
+            t, hist = ref_codec.compress_tiled_tensor(x, right=right, nbits=nbits, need_adjust=True)
+            back = t.materialize()
+            assert torch.equal(back.view(torch.int16), x.view(torch.int16))
+            d = digest_tensor(t)
+            d.update(path='triton_interpreter', seed=seed, shape=list(shape), right=right, nbits=nbits,
+                     hist=[int(v) for v in hist.tolist()])
+            codec_cases.append(d)
+            p = O.pack_block(x, right, nbits, need_hist=True)
+            assert scenarios._sha(p.invalid_exp) == d['invalid_exp'] and scenarios._sha(p.exp_data) == d['exp_data']
+            assert np.array_equal(O.unpack_block(p), O.as_u16(x))
+    # known answers: the survey's probe and the reference's validation fixture
+    torch.manual_seed(0)
+    x = (torch.randn(1, 8, 128, 128) * 0.7).to(torch.bfloat16)
+    x.view(-1)[5] = 0.0
+    rows, _ = ref_codec.compress_open_tiled_rows(x, right=127, nbits=3)
+    sealed = ref_codec.seal_open_tiled_rows(rows)
+    known = {'randn07_right127_nbits3': {'n_escapes': int(sealed.invalid_exp.numel()),
+                                         'exp_bytes': int(sealed.exp_data.numel())}}
+    torch.manual_seed(2026)
+    _q = torch.randn(1, 2, 1, 16).to(torch.bfloat16)
+    k = torch.randn(1, 2, 128, 16).to(torch.bfloat16)
+    v = torch.randn(1, 2, 128, 16).to(torch.bfloat16)
+    layer = ref_cache.float11Layer(3, 3, 3, 3, block_size=128, layout='legacy')
+    layer.update(k, v)
+    mem = layer.get_memory()
+    known['validation_fixture_seed2026_right3'] = {
+        'compressed_memory': int(mem['compressed_memory']), 'original_memory': int(mem['original_memory']),
+        'keys_outlier_ratios': float(mem['keys_outlier_ratios'])}
+    with open(os.path.join(HERE, 'codec_vectors.json'), 'w') as f:
+        json.dump({'cases': codec_cases, 'known_answers': known}, f, separators=(',', ':'))
+
+    # ---------------------------------------------------------------- adjuster vectors
+    rng = np.random.default_rng(0)
+    adj = []
+    for i in range(60):
+        h = np.zeros(256, np.int64)
+        centre, width = int(rng.integers(90, 150)), float(rng.uniform(0.5, 14))
+        idx = np.clip(np.round(rng.normal(centre, width, int(rng.integers(10, 50000)))).astype(int), 0, 255)
+        np.add.at(h, idx, 1)
+        if i % 4 == 0:
+            h[centre - 1] = h[centre] = h[centre + 1]
+        if i % 7 == 0:
+            h[:] = np.where(h > 0, h.max(), 0)
+        entry = {'hist': [int(v) for v in h]}
+        try:
+            entry['runtime'] = list(ref_cache.analysis_best_bits(torch.tensor(h)))
+        except IndexError:
+            entry['runtime'] = None
+        r, n = ref_calib.analysis_best_bits_coo([h.tolist()], ['x'])
+        entry['calibration'] = [int(r[0]), int(n[0])]
+        adj.append(entry)
+    for h in (np.zeros(256, np.int64), np.full(256, 3, np.int64)):
+        entry = {'hist': [int(v) for v in h]}
+        try:
+            entry['runtime'] = list(ref_cache.analysis_best_bits(torch.tensor(h)))
+        except IndexError:
+            entry['runtime'] = None
+        try:
+            r, n = ref_calib.analysis_best_bits_coo([h.tolist()], ['x'])
+            entry['calibration'] = [int(r[0]), int(n[0])]
+        except (IndexError, ZeroDivisionError):
+            entry['calibration'] = None      # the reference raises for these histograms
+        adj.append(entry)
+    # calibration JSON in the exporter's schema -> initial parameters
+    calib = {'c4': {}}
+    for l in range(3):
+        kx = synth.kv_tensor((1, 8, 512, 128), seed=100 + l, mu=-1 + l, key_offset=True)
+        vx = synth.kv_tensor((1, 8, 512, 128), seed=200 + l, mu=-1 + l)
+        calib['c4'][str(l)] = {
+            'prefill_keys': [int(v) for v in O.exponent_hist(kx)], 'decode_keys': [0] * 256,
+            'prefill_values': [int(v) for v in O.exponent_hist(vx)], 'decode_values': [0] * 256}
+    calib_path = os.path.join(HERE, 'calibration_kv.json')
+    with open(calib_path, 'w') as f:
+        json.dump(calib, f)
+    rights, nbits = ref_calib.export_initial_compress_parameters(calib_path)
+    mla_calib = {'c4': {'0': {'prefill_latent': calib['c4']['0']['prefill_keys'], 'decode_latent': [1] * 256,
+                              'prefill_rope': calib['c4']['1']['prefill_values'], 'decode_rope': [0] * 256}}}
+    mla_path = os.path.join(HERE, 'calibration_mla.json')
+    with open(mla_path, 'w') as f:
+        json.dump(mla_calib, f)
+    mla_rights, mla_nbits = ref_calib.export_initial_compress_parameters(mla_path)
+    with open(os.path.join(HERE, 'adjuster_vectors.json'), 'w') as f:
+        json.dump({'histograms': adj,
+                   'calibration_kv': {'rights': [list(map(int, r)) for r in rights], 'nbits': [list(map(int, n)) for n in nbits]},
+                   'calibration_mla': {'rights': [list(map(int, r)) for r in mla_rights],
+                                       'nbits': [list(map(int, n)) for n in mla_nbits]}}, f, separators=(',', ':'))
+
+    # ---------------------------------------------------------------- state machine
+    def fast_compress(x, right, nbits=3, seq_tile_size=128, tile_head_dim=None, need_adjust=False):
+        if x.shape[0] == 1:
+            if x.shape[-2] != seq_tile_size:
+                raise ValueError('Tiled compressed path currently requires seq_tile_size == seq_len per compressed block')
+            rows, hist = ref_codec.compress_open_tiled_rows(x, right=right, nbits=nbits, seq_tile_size=seq_tile_size,
+                                                            need_adjust=need_adjust)
+            return ref_codec.seal_open_tiled_rows(rows), (None if hist is None else hist.to(torch.int32))
+        p = O.pack_block(x, right, nbits, need_hist=need_adjust)
+        B, H, S, D = x.shape
+        t = ref_codec.TiledCompressedTensor(
+            sign_mass_data=torch.from_numpy(p.sign_mass_data), exp_data=torch.from_numpy(p.exp_data),
+            invalid_exp=torch.from_numpy(p.invalid_exp), tile_invalid_base=torch.from_numpy(p.tile_invalid_base),
+            left=p.left, right=right, nbits=nbits, original_shape=(B, H, S, D), seq_tile_size=seq_tile_size,
+            head_dim=D, tile_head_dim=D, tile_num_lanes=D // 8, num_sequence_tiles=1, num_kv_heads=H,
+            device=x.device)
+        return t, (None if p.hist is None else torch.from_numpy(p.hist).to(torch.int32))
+
+    def fast_materialize(state):
+        B, H, S, D = tuple(state['original_shape'])
+        p = O.PackedBlock(state['sign_mass_data'].numpy(), state['exp_data'].numpy(), state['invalid_exp'].numpy(),
+                          state['tile_invalid_base'].to(torch.int32).numpy(), int(state['left']), int(state['right']),
+                          int(state['nbits']), (B, H, S, D))
+        return torch.from_numpy(O.unpack_block(p).view(np.int16)).view(torch.bfloat16).view(B, H, S, D)
+
+    ref_cache.compress_tiled_tensor = fast_compress
+    ref_cache.materialize_tiled_state = fast_materialize
+
+    def make_cache(kind, cfg, **kw):
+        if kind == 'mla':
+            return ref_mla.MLAFloat11Cache(cfg, **kw)
+        return ref_cache.Float11Cache(cfg, **kw)
+
+    out = {}
+    for name, sc in scenarios.SCENARIOS.items():
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter('ignore')
+            digest, _ = scenarios.run_scenario(sc, make_cache, trace_every=16)
+        out[name] = digest
+        n_seg = [len(l['key_segments']) for l in digest['layers']]
+        print(name, 'segments', n_seg, 'params', [l['params'] for l in digest['layers']],
+              'updates', [(l['memory']['keys_update_times'], l['memory']['values_update_times']) for l in digest['layers']])
+    with open(os.path.join(HERE, 'state_machine.json'), 'w') as f:
+        json.dump(out, f, separators=(',', ':'))
+
+
+if __name__ == '__main__':
+    main()
