@@ -1,0 +1,21 @@
+"""adacode_b200 — the float11 lossless BF16 KV-cache path of AdaCode as sm_100a CUDA kernels
+behind the reference's HF-transformers Cache API.
+
+Public surface (same names as the reference package ``kv_compression``):
+  ``Float11Cache``, ``float11Layer``              float_cache_utils
+  ``MLAFloat11Cache``                             mla_float_cache_utils
+  ``compress_tiled_tensor``, ``materialize_tiled_state``, ``TiledCompressedTensor``   codec
+  ``export_initial_compress_parameters``          best_bit_analysis_kv_cache
+  ``model_config_map``                            model_configs
+"""
+from .best_bit_analysis_kv_cache import export_initial_compress_parameters
+from .codec import TiledCompressedTensor, compress_tiled_tensor, materialize_tiled_state
+from .float_cache_utils import Float11Cache, float11Layer
+from .mla_float_cache_utils import MLAFloat11Cache, MLALatentFloat11DenseRopeLayer
+from .model_configs import model_config_map
+
+__all__ = [
+    'Float11Cache', 'float11Layer', 'MLAFloat11Cache', 'MLALatentFloat11DenseRopeLayer',
+    'TiledCompressedTensor', 'compress_tiled_tensor', 'materialize_tiled_state',
+    'export_initial_compress_parameters', 'model_config_map',
+]
