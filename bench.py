@@ -1,0 +1,413 @@
+"""Benchmark of the float11 KV-cache hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config 1, "Qwen3-4B-shaped cache"): 36 layers x (K, V) of
+[1, 8, 20480, 128] bf16, per-layer sigma_c ~ LogNormal(mu_l, 1) with mu_l spread over [-1, 1],
+2 % outlier channels x30, a per-channel offset ~ N(0, 2) on K; windows and code lengths
+calibrated from a separately seeded tensor of the same distribution.  One STEP packs the whole
+cache (72 tensors, 160 blocks each, one pack launch per tensor) and unpacks it again.
+With N > 1 every rank owns one such sequence (sequences sharded across GPUs, weak scaling) and
+the per-layer exponent histograms are all-reduced once per step over NCCL, which is the only
+exchange the path has.
+
+Reported, in one JSON line on rank 0:
+  value     BF16-equivalent GB/s of the round trip with everything resident in HBM:
+            (bytes of bf16 packed + bytes of bf16 unpacked) / device time, summed over ranks
+  e2e       the same through the public API (Float11Cache.update / materialize_layer) with K/V
+            coming from pinned host memory and the unpacked tensors copied back to the host
+  roofline  the pack kernel (the slower of the two) against the measured HBM copy bandwidth
+  cpu_baseline  the CPU restatement of the reference's pack/unpack on the host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS, KV_HEADS, PROMPT, HEAD_DIM, BLOCK = 36, 8, 20480, 128, 128
+WORKLOAD = 'config1: Qwen3-4B-shaped cache, 36 layers x K,V [1,8,20480,128] bf16, prefill packed once then unpacked'
+METRIC = 'kv_pack_unpack_bf16_equiv_GBps'
+# DRAM bytes per element of one pack launch, from the ncu capture summarised in
+# profiles/k_pack_nbits3_16x8x8192x128.md (dram read + write) / elements; None until captured.
+PACK_DRAM_BYTES_PER_ELEM = None
+
+
+def synth_layer(layer: int, device, seed: int, which: str):
+    """One layer's K or V, generated on `device` from a seeded generator."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(1000 * seed + 2 * layer + (which == 'v'))
+    mu = -1.0 + 2.0 * layer / (LAYERS - 1)
+    sigma = torch.exp(mu + torch.randn(KV_HEADS, HEAD_DIM, generator=g, device=device))
+    sigma = torch.where(torch.rand(KV_HEADS, HEAD_DIM, generator=g, device=device) < 0.02, sigma * 30.0, sigma)
+    x = torch.randn(1, KV_HEADS, PROMPT, HEAD_DIM, generator=g, device=device) * sigma[None, :, None, :]
+    if which == 'k':
+        x = x + (2.0 * torch.randn(KV_HEADS, HEAD_DIM, generator=g, device=device))[None, :, None, :]
+    return x.to(torch.bfloat16)
+
+
+def calibrate(device):
+    """(right, nbits) per layer and tensor from seed-1 tensors, by the calibration rule; code
+    lengths above 4 (which the tiled cache rejects) fall back to the run-time adjuster's rule."""
+    import torch
+    from adacode_b200 import best_bit_analysis_kv_cache as calib
+    from adacode_b200 import codec
+    rights, nbits = [], []
+    for l in range(LAYERS):
+        pr, pn = [], []
+        for which in ('k', 'v'):
+            x = synth_layer(l, device, 1, which)[:, :, :2048]
+            hist = codec.exponent_hist(x).cpu().tolist()
+            r, n = calib.analysis_best_bits_coo([hist])
+            r, n = r[0], n[0]
+            if n > 4:
+                r, n = codec.analysis_best_bits(hist)
+            pr.append(r)
+            pn.append(n)
+        rights.append(tuple(pr))
+        nbits.append(tuple(pn))
+    return rights, nbits
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+              'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix='.csv')
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', f'--id={self.gpu_index}', f'--query-gpu={self.FIELDS}',
+                 '--format=csv,noheader,nounits', '-lms', '200'],
+                stdout=open(self.path, 'w'), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'samples': len(sm), 'reasons': sorted(reasons)}
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))['hbm_gbs']), 'measured'
+        except (KeyError, ValueError):
+            pass
+    return 6650.0, 'fallback'
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the restatement of the reference's pack/unpack on the host cores
+# --------------------------------------------------------------------------------------
+
+def cpu_round_trip(blocks_per_tensor: int, tensors: int, right=130, nbits=3, seed=0, repeats=1):
+    """Pack and unpack `tensors` tensors of `blocks_per_tensor` 128-token blocks of [1, 8, 128, 128]
+    with the OpenMP oracle, all blocks of a tensor in one call (handed over as a batch of blocks
+    so that every host thread has tiles to work on).  Returns (seconds, elements, threads)."""
+    import numpy as np
+    from oracle import float11_oracle as O
+    rng = np.random.default_rng(seed)
+    sigma = np.exp(rng.standard_normal((KV_HEADS, 1, HEAD_DIM))).astype(np.float32)
+    data = []
+    for t in range(tensors):
+        base = rng.standard_normal((blocks_per_tensor, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.float32) * sigma
+        data.append((base.view(np.uint32) >> 16).astype(np.uint16))     # bf16 by truncation
+    O.pack_block(data[0][:1], right, nbits)                             # load the library, warm the threads
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(repeats):
+        for x in data:
+            p = O.pack_block(x, right, nbits, need_hist=True)
+            y = O.unpack_block(p)
+            n += x.size
+    dt = time.perf_counter() - t0
+    assert np.array_equal(y, x)
+    return dt, n, O.num_threads()
+
+
+def run_reference_arm(args) -> None:
+    """The reference has no compiled code and its Python sources do not travel to the GPU box;
+    this arm times the CPU restatement of its pack/unpack (the oracle, pinned byte for byte to the
+    reference's own pack) on all host cores, on a bounded sample of the same workload."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    blocks = PROMPT // BLOCK
+    times, n = [], 0
+    for i in range(args.warmup + args.steps):
+        dt, n, threads = cpu_round_trip(blocks, 2, seed=i, repeats=LAYERS)   # K and V of every layer
+        if i >= args.warmup:
+            times.append(dt)
+    t = sum(times) / len(times)
+    value = 2 * 2 * n / t / 1e9
+    sample = (f'whole workload per step: {LAYERS} layers x K,V [1,8,20480,128] packed and unpacked '
+              '(one layer\'s random data reused for every layer)')
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': round(value, 3), 'unit': 'GB/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(t * 1e3, 3), 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
+        'config': {'workload': WORKLOAD, 'sample': sample},
+        'cpu_baseline': {'value': round(value, 3), 'unit': 'GB/s', 'cores': threads, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': round(value, 3), 'unit': 'GB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+
+class PackedTensorSlots:
+    """Preallocated outputs of one tensor's pack launch (raw C-ABI use: no allocation and no
+    host read inside the timed region)."""
+
+    def __init__(self, x, right, nbits, device):
+        import torch
+        from adacode_b200 import codec
+        self.x, self.right, self.nbits = x, int(right), int(nbits)
+        self.left = self.right - 2 ** self.nbits + 1
+        chunk, _ = codec.pack_blocks(x, right, nbits, BLOCK)            # sizing pass (also a warm-up)
+        self.n_blocks = chunk.n_blocks
+        self.n_escapes = chunk.n_escapes
+        self.sign_mant, self.codes, self.tile_base = chunk.sign_mant, chunk.codes, chunk.tile_base
+        self.escapes = torch.empty(max(self.n_escapes, 16), dtype=torch.uint8, device=device)
+        self.meta = torch.zeros(self.n_blocks + 2, dtype=torch.int64, device=device)
+
+
+def run_gpu_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from adacode_b200 import Float11Cache, _lib, codec
+    from tests.scenarios import StubConfig
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    L = _lib.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    rights, nbits = calibrate(dev)
+    slots = []
+    for l in range(LAYERS):
+        for wi, which in enumerate(('k', 'v')):
+            x = synth_layer(l, dev, 7 * rank, which)
+            slots.append(PackedTensorSlots(x, rights[l][wi], nbits[l][wi], dev))
+    n_elems = sum(s.x.numel() for s in slots)
+    n_esc = sum(s.n_escapes for s in slots)
+    code_bytes = sum(s.x.numel() * s.nbits // 8 for s in slots)
+    tiles = 1 * KV_HEADS * (PROMPT // BLOCK)
+    ws = codec._scratch_for(dev).workspace_for(tiles, BLOCK * HEAD_DIM)
+    hists = torch.zeros((LAYERS * 2, 256), dtype=torch.int32, device=dev)
+    status = codec._scratch_for(dev).status
+    out = [torch.empty((1, KV_HEADS, PROMPT, HEAD_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    sb, sh, ss, _ = slots[0].x.stride()
+    db, dh, ds, _ = out[0].stride()
+
+    def pack_all():
+        for i, s in enumerate(slots):
+            rc = L.adacode_pack_tiles(s.x.data_ptr(), sb, sh, ss, 1, KV_HEADS, s.n_blocks, BLOCK, HEAD_DIM, s.right,
+                                      s.nbits, s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr(),
+                                      s.escapes.numel(), s.tile_base.data_ptr(), s.meta.data_ptr(),
+                                      hists[i].data_ptr(), ws.data_ptr(), ws.numel(),
+                                      s.meta.data_ptr() + 8 * (s.n_blocks + 1), stream)
+            if rc:
+                _lib.check(rc, 'adacode_pack_tiles')
+
+    def unpack_all():
+        for i, s in enumerate(slots):
+            rc = L.adacode_unpack_tiles(s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr(),
+                                        s.escapes.numel(), s.tile_base.data_ptr(), s.meta.data_ptr(), 1, KV_HEADS,
+                                        s.n_blocks, BLOCK, HEAD_DIM, s.left, s.nbits, out[i & 1].data_ptr(), db, dh, ds,
+                                        status.data_ptr(), stream)
+            if rc:
+                _lib.check(rc, 'adacode_unpack_tiles')
+
+    def step(ev=None):
+        hists.zero_()
+        if ev:
+            ev[0].record()
+        pack_all()
+        if ev:
+            ev[1].record()
+        if world > 1:
+            dist.all_reduce(hists)          # every shard sees the histogram of the whole batch
+        unpack_all()
+        if ev:
+            ev[2].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_begin.elapsed_time(t_end)
+    pack_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    unpack_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+
+    # correctness of what was just timed: the last two tensors unpacked, and the status word
+    for i in (len(slots) - 2, len(slots) - 1):
+        assert torch.equal(out[i & 1].view(torch.int16), slots[i].x.view(torch.int16)), 'round trip not bit-exact'
+    codec.check_device_status(dev)
+
+    # ---- end to end through the public API, K/V in pinned host memory -------------------
+    cfg = StubConfig(LAYERS)
+    host_in = [s.x.to('cpu').pin_memory() for s in slots]
+    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(2)]
+    stage = [torch.empty_like(slots[0].x) for _ in range(2)]
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step():
+        cache = Float11Cache(cfg, right=rights, exp_bits=nbits, need_adjust=True, update_steps=128,
+                             residual_length=0, block_size=BLOCK, layout='segmented_tiled')
+        for l in range(LAYERS):
+            stage[0].copy_(host_in[2 * l], non_blocking=True)
+            stage[1].copy_(host_in[2 * l + 1], non_blocking=True)
+            cache.update(stage[0], stage[1], l)
+        for l in range(LAYERS):
+            dk, dv = cache.materialize_layer(l)
+            host_out[0].copy_(dk, non_blocking=True)
+            host_out[1].copy_(dv, non_blocking=True)
+        torch.cuda.synchronize(dev)
+        return cache
+
+    e2e_step()
+    barrier()
+    w0 = torch.cuda.Event(enable_timing=True)
+    w1 = torch.cuda.Event(enable_timing=True)
+    w0.record()
+    for _ in range(e2e_steps):
+        cache = e2e_step()
+    w1.record()
+    barrier()
+    e2e_ms = w0.elapsed_time(w1) / e2e_steps
+    assert torch.equal(host_out[1].view(torch.int16), host_in[-1].view(torch.int16)), 'e2e round trip not bit-exact'
+    mem = cache.get_memory()
+    ratio = mem['kv_compressed_memory'] / mem['kv_original_memory']
+
+    times = torch.tensor([total_ms, pack_ms, unpack_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, pack_ms, unpack_ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        bf16_bytes = 2.0 * n_elems
+        ms_per_step = total_ms / args.steps
+        value = world * 2 * bf16_bytes / (ms_per_step * 1e-3) / 1e9
+        alg_pack = 2.0 * n_elems + n_elems + code_bytes + n_esc          # read bf16, write planes + escapes
+        peak, peak_kind = measured_hbm_peak()
+        launches = len(slots)
+        ach_pack = alg_pack / (pack_ms * 1e-3) / 1e9
+        ach_unpack = alg_pack / (unpack_ms * 1e-3) / 1e9
+        cpu_dt, cpu_n, cpu_threads = cpu_round_trip(PROMPT // BLOCK, 2, repeats=max(1, LAYERS // 6))
+        line = {
+            'metric': METRIC, 'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
+            'config': {'workload': WORKLOAD, 'per_gpu': 'one 20480-token sequence per GPU', 'block_size': BLOCK,
+                       'l2': 'inputs (3.0 GB per GPU) exceed L2, no flush needed',
+                       'nbits_histogram': {str(n): sum(1 for s in slots if s.nbits == n) for n in (1, 2, 3, 4)},
+                       'escape_fraction': round(n_esc / n_elems, 5)},
+            'pack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (pack_ms * 1e-3) / 1e9, 1),
+            'unpack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (unpack_ms * 1e-3) / 1e9, 1),
+            'compression_ratio': round(ratio, 5),
+            'roofline': {'bound': 'hbm', 'kernel': 'k_pack (+ k_compact_escapes)', 'achieved': round(ach_pack, 1),
+                         'peak': peak, 'unit': 'GB/s', 'frac': round(ach_pack / peak, 4), 'peak_source': peak_kind,
+                         'traffic': None if PACK_DRAM_BYTES_PER_ELEM is None else
+                         round(PACK_DRAM_BYTES_PER_ELEM * n_elems / launches),
+                         'algorithmic_bytes_per_launch': round(alg_pack / launches),
+                         'avg_launch_us': round(pack_ms * 1e3 / launches, 2)},
+            'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_uniform', 'achieved': round(ach_unpack, 1),
+                                'peak': peak, 'unit': 'GB/s', 'frac': round(ach_unpack / peak, 4),
+                                'avg_launch_us': round(unpack_ms * 1e3 / launches, 2)},
+            'cpu_baseline': {'value': round(2 * 2 * cpu_n / cpu_dt / 1e9, 3), 'unit': 'GB/s', 'cores': cpu_threads,
+                             'kind': 'port', 'sample': f'{max(1, LAYERS // 6)} of {LAYERS} layers, K and V '
+                             '[1,8,20480,128], packed and unpacked by the OpenMP oracle'},
+            'e2e': {'value': round(world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9, 2), 'unit': 'GB/s',
+                    'h2d_bytes_per_step': int(bf16_bytes), 'd2h_bytes_per_step': int(bf16_bytes),
+                    'ms_per_step': round(e2e_ms, 2), 'api': 'Float11Cache.update + materialize_layer'},
+            'gpu_launches': args.steps * len(slots) * 3,
+            'clocks': clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == '__main__':
+    main()
