@@ -11,6 +11,7 @@
 // Both kernels are bandwidth work: no tensor cores, no reshaping into GEMMs.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "adacode.h"
@@ -763,6 +764,8 @@ __global__ void k_choose_params(const int32_t *__restrict__ hists, int n_hists, 
     }
 }
 
+#include "adacode_pipeline.cuh"
+
 void stable_order_desc(const int64_t *hist, int *order) {
     for (int i = 0; i < 256; ++i) order[i] = i;
     for (int i = 1; i < 256; ++i) {
@@ -810,6 +813,41 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 int grid_for(int64_t n_tiles, int ctas_per_sm) {
     const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
     return (int)(n_tiles < cap ? n_tiles : cap);
+}
+
+
+bool pipeline_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = getenv("ADACODE_DISABLE_PIPELINE");
+        cached = (e && e[0] == '1') ? 0 : 1;
+    }
+    return cached == 1;
+}
+
+// The pipelined kernels move whole units with bulk copies: 16-byte aligned planes, head_dim a
+// multiple of 16 and at most 2048, token rows in multiples of 8.
+bool pipeline_shape_ok(int seq_tile, int D) { return D % 16 == 0 && D <= 2048 && seq_tile % 8 == 0; }
+
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, size_t bytes) {
+    // per device and kernel; the attribute call is cheap but not free
+    static thread_local const void *last_kernel[16] = {nullptr};
+    int dev = 0;
+    ADACODE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 16 && last_kernel[dev] == (const void *)kernel) return ADACODE_OK;
+    ADACODE_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (dev >= 0 && dev < 16) last_kernel[dev] = (const void *)kernel;
+    return ADACODE_OK;
+}
+
+int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
+    int rc = ensure_dynamic_smem(k_unpack_pipe, sizeof(UnpackSmem));
+    if (rc != ADACODE_OK) return rc;
+    const int grid = grid_for(a.n_tiles, 2);
+    k_unpack_pipe<<<grid, kPipeThreads, sizeof(UnpackSmem), st>>>(a);
+    ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
 }
 
 template <int N, int CH>
@@ -943,8 +981,18 @@ int adacode_unpack_tiles(const uint8_t *sign_mant, const uint8_t *codes, const u
     u.dst = (uint16_t *)dst_bf16;
     u.db = dstride_b, u.dh = dstride_h, u.ds = dstride_s;
     u.status = status;
-    const int grid = grid_for(n_tiles, 6);
     cudaStream_t st = (cudaStream_t)stream;
+    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D)) {
+        UnpackPipeArgs pa;
+        pa.sign_mant = sign_mant, pa.codes = codes, pa.escapes = escapes, pa.escapes_len = escapes_len;
+        pa.tile_base = tile_base, pa.seg_off = seg_escape_offsets, pa.left = left, pa.nbits = nbits;
+        pa.seg = nullptr;
+        pa.H = H, pa.BH = B * H, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = seq_tile * D;
+        pa.n_tiles = n_tiles, pa.dst = (uint16_t *)dst_bf16;
+        pa.db = dstride_b, pa.dh = dstride_h, pa.ds = dstride_s, pa.status = status;
+        return launch_unpack_pipe(pa, st);
+    }
+    const int grid = grid_for(n_tiles, 6);
     if (D % 16 == 0)
         k_unpack_uniform<16><<<grid, kThreads, 0, st>>>(u, sign_mant, codes, escapes, escapes_len, tile_base,
                                                         seg_escape_offsets, n_tiles, left, nbits);
@@ -970,8 +1018,18 @@ int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments,
     u.dst = (uint16_t *)dst_bf16;
     u.db = dstride_b, u.dh = dstride_h, u.ds = dstride_s;
     u.status = status;
-    const int grid = grid_for(n_tiles, 6);
     cudaStream_t st = (cudaStream_t)stream;
+    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D)) {
+        UnpackPipeArgs pa;
+        pa.sign_mant = nullptr, pa.codes = nullptr, pa.escapes = nullptr, pa.escapes_len = 0;
+        pa.tile_base = nullptr, pa.seg_off = nullptr, pa.left = 0, pa.nbits = 0;
+        pa.seg = segments_dev;
+        pa.H = H, pa.BH = B * H, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = seq_tile * D;
+        pa.n_tiles = n_tiles, pa.dst = (uint16_t *)dst_bf16;
+        pa.db = dstride_b, pa.dh = dstride_h, pa.ds = dstride_s, pa.status = status;
+        return launch_unpack_pipe(pa, st);
+    }
+    const int grid = grid_for(n_tiles, 6);
     if (D % 16 == 0) k_unpack_segments<16><<<grid, kThreads, 0, st>>>(u, segments_dev, n_tiles);
     else k_unpack_segments<8><<<grid, kThreads, 0, st>>>(u, segments_dev, n_tiles);
     ADACODE_CUDA_TRY(cudaGetLastError());

@@ -42,6 +42,8 @@ extern "C" {
 /* bits OR-ed into the device status word */
 #define ADACODE_STATUS_ESCAPE_OVERFLOW 1 /* pack: escapes_capacity too small, stream truncated */
 #define ADACODE_STATUS_ESCAPE_UNDERRUN 2 /* unpack: a tile wanted an escape beyond n_escapes */
+#define ADACODE_STATUS_TIMEOUT 4         /* a bounded on-chip wait gave up; results are invalid */
+#define ADACODE_STATUS_MISALIGNED 8      /* a plane pointer inside a segment record is not 16-byte aligned */
 
 /* Library version, major*10000 + minor*100 + patch. */
 int adacode_version(void);
