@@ -809,6 +809,9 @@ int choose_host(const int64_t *hist, int n_lo, int n_hi, bool escape_slot, int *
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+size_t unit_counts_bytes(int64_t n_tiles, int64_t tile_elems) {
+    return align_up((size_t)n_tiles * (size_t)(tile_elems / 128 + 1) * 4, 256);
+}
 
 int grid_for(int64_t n_tiles, int ctas_per_sm) {
     const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
@@ -850,6 +853,31 @@ int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
     return ADACODE_OK;
 }
 
+template <int N>
+int launch_pack_pipe_n(const PackPipeArgs &pa, cudaStream_t st) {
+    const int grid = grid_for(pa.base.n_tiles, 2);
+    if (pa.base.hist) {
+        int rc = ensure_dynamic_smem(k_pack_pipe<N, true>, sizeof(PackSmem));
+        if (rc != ADACODE_OK) return rc;
+        k_pack_pipe<N, true><<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+    } else {
+        int rc = ensure_dynamic_smem(k_pack_pipe<N, false>, sizeof(PackSmem));
+        if (rc != ADACODE_OK) return rc;
+        k_pack_pipe<N, false><<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+    }
+    ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
+}
+
+int launch_pack_pipe(const PackPipeArgs &pa, int nbits, cudaStream_t st) {
+    switch (nbits) {
+        case 1: return launch_pack_pipe_n<1>(pa, st);
+        case 2: return launch_pack_pipe_n<2>(pa, st);
+        case 3: return launch_pack_pipe_n<3>(pa, st);
+        default: return launch_pack_pipe_n<4>(pa, st);
+    }
+}
+
 template <int N, int CH>
 void launch_pack(const PackArgs &a, int grid, cudaStream_t st) {
     if (a.hist) k_pack<N, CH, true><<<grid, kThreads, 0, st>>>(a);
@@ -882,8 +910,10 @@ const char *adacode_last_cuda_error(void) { return g_last_cuda_error; }
 
 size_t adacode_pack_workspace_bytes(int64_t n_tiles, int64_t tile_elems) {
     if (n_tiles <= 0 || tile_elems <= 0) return 256;
-    // [done counter, padded to 256][tile_counts int32][escape scratch]
-    return 256 + align_up((size_t)n_tiles * 4, 256) + (size_t)n_tiles * (size_t)tile_elems;
+    // [done counter, padded to 256][tile_counts int32][unit_counts int32][escape scratch]
+    // a tile has at most tile_elems / 128 units (a unit is at least 8 rows of at least 16 elements)
+    return 256 + align_up((size_t)n_tiles * 4, 256) + unit_counts_bytes(n_tiles, tile_elems) +
+           (size_t)n_tiles * (size_t)tile_elems;
 }
 
 int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s, int B, int H,
@@ -923,12 +953,32 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
     a.codes = codes;
     a.done = (unsigned int *)ws;
     a.tile_counts = (int32_t *)(ws + 256);
-    a.esc_scratch = ws + 256 + align_up((size_t)n_tiles * 4, 256);
+    int32_t *unit_counts = (int32_t *)(ws + 256 + align_up((size_t)n_tiles * 4, 256));
+    a.esc_scratch = ws + 256 + align_up((size_t)n_tiles * 4, 256) + unit_counts_bytes(n_tiles, tile_elems);
     a.tile_base = tile_base;
     a.seg_off = seg_escape_offsets;
     a.n_blocks = n_blocks;
     a.hist = hist256;
 
+    const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 8
+                                ? (n_tiles + kWarps - 1) / kWarps
+                                : (int64_t)sm_count() * 8);
+    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D)) {
+        PackPipeArgs pa;
+        pa.base = a;
+        pa.unit_counts = unit_counts;
+        pa.unit_rows = unit_rows_for(seq_tile, D);
+        pa.units_per_tile = (seq_tile + pa.unit_rows - 1) / pa.unit_rows;
+        pa.status = status;
+        int rc = launch_pack_pipe(pa, nbits, st);
+        if (rc != ADACODE_OK) return rc;
+        k_compact_units<<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
+                                                    seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
+                                                    pa.unit_rows * D, pa.units_per_tile, escapes, escapes_capacity,
+                                                    hist256, status);
+        ADACODE_CUDA_TRY(cudaGetLastError());
+        return ADACODE_OK;
+    }
     const int grid = grid_for(n_tiles, 4);
     if (CH == 16) {
         switch (nbits) {
@@ -946,9 +996,6 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
         }
     }
     ADACODE_CUDA_TRY(cudaGetLastError());
-    const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 8
-                                ? (n_tiles + kWarps - 1) / kWarps
-                                : (int64_t)sm_count() * 8);
     k_compact_escapes<<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, tile_base, seg_escape_offsets,
                                                   n_tiles, a.BH, a.tile_elems, escapes, escapes_capacity, status);
     ADACODE_CUDA_TRY(cudaGetLastError());

@@ -3,7 +3,7 @@
 // while the current unit is processed, and results leave through shared memory with bulk
 // stores.  Included by adacode_kernels.cu inside its anonymous namespace.
 //
-// One CTA = 8 consumer warps + 1 producer warp, persistent over tiles.  A "unit" is a run of
+// One CTA = 16 consumer warps + 1 producer warp, persistent over tiles.  A "unit" is a run of
 // whole token rows of one tile, at most 16384 elements (a whole 128 x 128 tile).
 //   producer warp : waits for a free stage, issues the unit's bulk loads (sign/mantissa and
 //                   code planes, or source rows) against the stage's "full" mbarrier, and
@@ -15,7 +15,9 @@
 // kernel still reaches every barrier and terminates).
 #pragma once
 
-constexpr int kConsumerThreads = 256;
+constexpr int kPCPT = 2;                                   // 16-element chunks per consumer thread and unit
+constexpr int kPWarps = 1024 / (32 * kPCPT);                // consumer warps
+constexpr int kConsumerThreads = kPWarps * 32;
 constexpr int kPipeThreads = kConsumerThreads + 32;
 constexpr int kUnitElems = 16384;
 constexpr int kStages = 2;
@@ -69,7 +71,40 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // makes shared-memory writes of this thread visible to the async proxy (bulk stores)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+// Inclusive warp scan of kPCPT per-lane counters walked in (k, lane) order (counters <= 16 each, so
+// they travel as 16-bit fields).  incl[k] = inclusive rank of (k, lane) within the warp's
+// kPCPT x 32 chunks; returns the warp total.
+__device__ __forceinline__ int warp_scan_counts(const int (&cnt)[kPCPT], int (&incl)[kPCPT]) {
+    static_assert(kPCPT == 2 || kPCPT == 4, "two or four chunks per thread");
+    const int lane = threadIdx.x & 31;
+    uint32_t a = (uint32_t)cnt[0] | ((uint32_t)cnt[1] << 16);
+    uint32_t b = 0;
+    if (kPCPT == 4) b = (uint32_t)cnt[kPCPT - 2] | ((uint32_t)cnt[kPCPT - 1] << 16);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t ua = __shfl_up_sync(kFull, a, d);
+        uint32_t ub = 0;
+        if (kPCPT == 4) ub = __shfl_up_sync(kFull, b, d);
+        if (lane >= d) {
+            a += ua;
+            b += ub;
+        }
+    }
+    const uint32_t ta = __shfl_sync(kFull, a, 31);
+    const int t0 = ta & 0xFFFF, t1 = ta >> 16;
+    incl[0] = (int)(a & 0xFFFF);
+    incl[1] = (int)(a >> 16) + t0;
+    int total = t0 + t1;
+    if (kPCPT == 4) {
+        const uint32_t tb = __shfl_sync(kFull, b, 31);
+        incl[kPCPT - 2] = (int)(b & 0xFFFF) + total;
+        incl[kPCPT - 1] = (int)(b >> 16) + total + (int)(tb & 0xFFFF);
+        total += (int)(tb & 0xFFFF) + (int)(tb >> 16);
+    }
+    return total;
+}
 
 // Rows of one tile handled per unit: whole rows, a multiple of 8 (so that code bytes per unit are a
 // multiple of 16), at most kUnitElems elements.
@@ -111,7 +146,7 @@ struct alignas(128) UnpackSmem {
     alignas(128) uint16_t out[kUnitElems];
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
-    int warp_tot[kWarps];
+    int warp_tot[kPWarps];
 };
 static_assert(sizeof(UnpackStage) % 128 == 0, "stage buffers must stay 128-byte aligned");
 
@@ -184,12 +219,12 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     const int chunks = m.elems >> 4;
     const uint32_t left2 = ((uint32_t)m.left & 0xFFu) * 0x10001u;
 
-    uint4 o[kCPT][2];
-    uint32_t zm[kCPT][2];
-    int zc[kCPT];
+    uint4 o[kPCPT][2];
+    uint32_t zm[kPCPT][2];
+    int zc[kPCPT];
 #pragma unroll
-    for (int k = 0; k < kCPT; ++k) {
-        const int c = warp * (kCPT * 32) + k * 32 + lane;
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
         uint32_t g[2] = {0u, 0u};
         uint4 sv = make_uint4(0, 0, 0, 0);
         const bool valid = c < chunks;
@@ -213,21 +248,21 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
             o[k][q].w = assemble2(__byte_perm(s1, 0u, 0x4342), cd[6], cd[7], left2);
         }
     }
-    int incl[kCPT];
-    const int wtot = warp_scan4(zc, incl);
+    int incl[kPCPT];
+    const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;
     bulk_wait_read();          // the previous unit's store has finished reading s.out
     consumer_sync();
     int wprefix = 0, unit_tot = 0;
 #pragma unroll
-    for (int i = 0; i < kWarps; ++i) {
+    for (int i = 0; i < kPWarps; ++i) {
         const int t = s.warp_tot[i];
         wprefix += (i < warp) ? t : 0;
         unit_tot += t;
     }
 #pragma unroll
-    for (int k = 0; k < kCPT; ++k) {
-        const int c = warp * (kCPT * 32) + k * 32 + lane;
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
         if (c < chunks) {
             uint4 *w = reinterpret_cast<uint4 *>(s.out + c * 16);
             w[0] = o[k][0];
@@ -273,7 +308,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     }
 }
 
-__global__ void __launch_bounds__(kPipeThreads) k_unpack_pipe(const UnpackPipeArgs a) {
+__global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPipeArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     UnpackSmem &s = *reinterpret_cast<UnpackSmem *>(smem_raw);
     const int tid = threadIdx.x;
@@ -369,4 +404,368 @@ __global__ void __launch_bounds__(kPipeThreads) k_unpack_pipe(const UnpackPipeAr
         }
     }
     bulk_wait_all();
+}
+
+// ---------------------------------------------------------------------------------------
+// pack
+// ---------------------------------------------------------------------------------------
+
+// In-window histogram over several group words at once.  The match bit of a code lands on the
+// least significant bit of its N-bit slot, so N groups (4 for N <= 2) can be overlaid on one
+// 32-bit word before the population count: one lop3 + popc + add per code value for up to
+// 32 elements.
+template <int N>
+struct GroupsPerWord { static constexpr int v = (N == 3) ? 3 : 4; };
+
+template <int N>
+__device__ __forceinline__ uint32_t overlay_shift(int j) {
+    if (N >= 3) return (uint32_t)j;                           // sub-slot offsets 0..N-1
+    if (N == 2) return (uint32_t)((j & 1) + 16 * (j >> 1));   // 16-bit halves, two sub-slot offsets
+    return (uint32_t)(8 * j);                                 // N == 1: one byte per group
+}
+
+template <int N, int NG>
+__device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], uint32_t (&cnt)[1 << N]) {
+    constexpr int GPW = GroupsPerWord<N>::v;
+    constexpr uint32_t M = SlotLsb<N>::v;
+#pragma unroll
+    for (int base = 0; base < NG; base += GPW) {
+        uint32_t plane[N];
+        uint32_t used = 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) plane[i] = 0;
+#pragma unroll
+        for (int j = 0; j < GPW; ++j) {
+            if (base + j < NG) {
+                const uint32_t sh = overlay_shift<N>(j);
+                used |= M << sh;
+#pragma unroll
+                for (int i = 0; i < N; ++i) plane[i] |= ((g[base + j] >> i) & M) << sh;
+            }
+        }
+#pragma unroll
+        for (int v = 1; v < (1 << N); ++v) {
+            uint32_t m = used;
+#pragma unroll
+            for (int i = 0; i < N; ++i) m &= ((v >> i) & 1) ? plane[i] : ~plane[i];
+            cnt[v] += __popc(m);
+        }
+    }
+}
+
+constexpr int kPackEscStage = kUnitElems;   // worst case: every element of a unit escapes
+
+struct PackUnitMeta {
+    uint8_t *sm_dst;       // sign/mantissa bytes of the unit
+    uint8_t *code_dst;     // code bytes of the unit
+    uint8_t *esc_dst;      // the unit's escape slot in the scratch
+    int32_t *unit_count;   // where the unit's escape count goes
+    int32_t *tile_count;   // where the tile's escape count goes (written with the last unit)
+    int elems;
+    int first_unit_of_tile;
+    int last_unit_of_tile;
+};
+
+struct alignas(128) PackStage {
+    alignas(128) uint16_t in[kUnitElems];
+    alignas(16) PackUnitMeta meta;
+};
+
+struct alignas(128) PackSmem {
+    PackStage stage[kStages];
+    alignas(128) uint8_t sm[kUnitElems];
+    alignas(128) uint8_t codes[kUnitElems / 2];
+    alignas(128) uint8_t esc[kPackEscStage];
+    alignas(8) uint64_t full[kStages];
+    alignas(8) uint64_t empty[kStages];
+    int warp_tot[kPWarps];
+    int hist[256];
+    int is_last;
+    long long carry;
+    int scan[kPWarps];
+};
+static_assert(sizeof(PackStage) % 128 == 0, "stage buffers must stay 128-byte aligned");
+
+struct PackPipeArgs {
+    PackArgs base;            // the fields shared with the direct kernel
+    int32_t *unit_counts;     // n_tiles * units_per_tile
+    int unit_rows, units_per_tile;
+    int32_t *status;
+};
+
+// Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets.
+// Run by the 256 consumer threads of the CTA that finished last.
+__device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s_carry, int *s_scan) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        *s_carry = 0;
+        a.seg_off[0] = 0;
+    }
+    consumer_sync();
+    for (int64_t base = 0; base < a.n_tiles; base += kConsumerThreads) {
+        const int64_t t = base + tid;
+        int x = (t < a.n_tiles) ? __ldcg(a.tile_counts + t) : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(kFull, x, d);
+            if (lane >= d) x += u;
+        }
+        if (lane == 31) s_scan[warp] = x;
+        consumer_sync();
+        int wp = 0, tot = 0;
+#pragma unroll
+        for (int i = 0; i < kPWarps; ++i) {
+            const int v = s_scan[i];
+            wp += (i < warp) ? v : 0;
+            tot += v;
+        }
+        const long long incl = *s_carry + wp + x;
+        if (t < a.n_tiles) {
+            a.tile_base[t] = (int32_t)incl;
+            if ((t + 1) % a.BH == 0) a.seg_off[(t + 1) / a.BH] = incl;
+        }
+        consumer_sync();
+        if (tid == 0) *s_carry += tot;
+        consumer_sync();
+    }
+    __threadfence_block();
+    for (int64_t t = tid; t < a.n_tiles; t += kConsumerThreads) {
+        const int64_t blk = t / a.BH;
+        if (blk > 0) a.tile_base[t] -= (int32_t)a.seg_off[blk];
+    }
+    if (tid == 0) *a.done = 0u;
+}
+
+template <int N, bool HIST>
+__device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint64_t *empty_bar, int left,
+                                          int &running, uint32_t (&cnt)[1 << N]) {
+    constexpr int CB = 2 * N;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const PackUnitMeta m = st.meta;
+    if (m.first_unit_of_tile) running = 0;
+    const int chunks = m.elems >> 4;
+
+    uint4 smv[kPCPT];
+    uint32_t g[kPCPT * 2], zm[kPCPT][2];
+    int zc[kPCPT];
+#pragma unroll
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        const bool valid = c < chunks;
+        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+        if (valid) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(st.in + c * 16);
+            w0 = p[0];
+            w1 = p[1];
+        }
+        const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wb[4] = {w1.x, w1.y, w1.z, w1.w};
+        g[2 * k] = valid ? encode_group<N>(wa, left) : 0u;
+        g[2 * k + 1] = valid ? encode_group<N>(wb, left) : 0u;
+        zm[k][0] = valid ? zero_slots<N>(g[2 * k]) : 0u;
+        zm[k][1] = valid ? zero_slots<N>(g[2 * k + 1]) : 0u;
+        zc[k] = __popc(zm[k][0]) + __popc(zm[k][1]);
+        smv[k].x = signmant4(w0.x, w0.y);
+        smv[k].y = signmant4(w0.z, w0.w);
+        smv[k].z = signmant4(w1.x, w1.y);
+        smv[k].w = signmant4(w1.z, w1.w);
+    }
+    if (HIST) count_codes_overlaid<N, kPCPT * 2>(g, cnt);
+
+    int incl[kPCPT];
+    const int wtot = warp_scan_counts(zc, incl);
+    if (lane == 0) s.warp_tot[warp] = wtot;
+    bulk_wait_read();      // the previous unit's stores have finished reading the out buffers
+    consumer_sync();
+    int wprefix = 0, unit_tot = 0;
+#pragma unroll
+    for (int i = 0; i < kPWarps; ++i) {
+        const int t = s.warp_tot[i];
+        wprefix += (i < warp) ? t : 0;
+        unit_tot += t;
+    }
+#pragma unroll
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        if (c < chunks) {
+            *reinterpret_cast<uint4 *>(s.sm + c * 16) = smv[k];
+            const uint32_t gg[2] = {g[2 * k], g[2 * k + 1]};
+            store_chunk_codes<N, 16>(s.codes + c * CB, gg);
+            if (zc[k] != 0) {
+                uint8_t *out = s.esc + wprefix + incl[k] - zc[k];
+                const uint16_t *src = st.in + c * 16;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t z = zm[k][q];
+                    while (z) {
+                        const int pos = 31 - __clz(z);
+                        z ^= 1u << pos;
+                        const uint32_t e = (src[q * 8 + 7 - pos / N] >> 7) & 0xFFu;
+                        *out++ = (uint8_t)e;
+                    }
+                }
+            }
+        }
+    }
+    mbar_arrive(empty_bar);
+    fence_async_smem();
+    consumer_sync();
+    running += unit_tot;
+    if (tid == 0) {
+        if (m.elems > 0) {
+            bulk_store(m.sm_dst, s.sm, (uint32_t)m.elems);
+            bulk_store(m.code_dst, s.codes, (uint32_t)m.elems * N / 8);
+            if (unit_tot > 0) bulk_store(m.esc_dst, s.esc, (uint32_t)((unit_tot + 15) & ~15));
+            bulk_commit();
+        }
+        *m.unit_count = unit_tot;
+        if (m.last_unit_of_tile) *m.tile_count = running;
+    }
+}
+
+template <int N, bool HIST>
+__global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArgs pa) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    PackSmem &s = *reinterpret_cast<PackSmem *>(smem_raw);
+    const PackArgs &a = pa.base;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], kConsumerThreads);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (HIST && tid < 256) s.hist[tid] = 0;
+    __syncthreads();
+
+    const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
+    const bool rows_contig = (a.ss == a.D);
+
+    if (tid >= kConsumerThreads) {
+        // ---------------- producer warp ----------------
+        const int lane = tid & 31;
+        uint32_t it = 0;
+        for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+            const int64_t blk = tile / a.BH;
+            const int bh = (int)(tile - blk * a.BH);
+            const int b = bh / a.H, h = bh - b * a.H;
+            const uint16_t *tsrc = a.src + (int64_t)b * a.sb + (int64_t)h * a.sh + blk * a.seq_tile * a.ss;
+            for (int u = 0; u < upt; ++u, ++it) {
+                const int stg = it % kStages;
+                PackStage &st = s.stage[stg];
+                mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, pa.status);
+                const int row0 = u * unit_rows;
+                const int rows = min(unit_rows, a.seq_tile - row0);
+                const int elems = rows * a.D;
+                if (lane == 0) {
+                    PackUnitMeta &m = st.meta;
+                    const int64_t e0 = tile * a.tile_elems + (int64_t)row0 * a.D;
+                    m.sm_dst = a.sign_mant + e0;
+                    m.code_dst = a.codes + e0 * N / 8;
+                    m.esc_dst = a.esc_scratch + e0;
+                    m.unit_count = pa.unit_counts + tile * upt + u;
+                    m.tile_count = a.tile_counts + tile;
+                    m.elems = elems;
+                    m.first_unit_of_tile = (u == 0);
+                    m.last_unit_of_tile = (u == upt - 1);
+                    mbar_arrive_expect_tx(&s.full[stg], (uint32_t)elems * 2u);
+                }
+                __syncwarp();
+                const uint16_t *usrc = tsrc + (int64_t)row0 * a.ss;
+                if (rows_contig) {
+                    if (lane == 0) bulk_load(st.in, usrc, (uint32_t)elems * 2u, &s.full[stg]);
+                } else {
+                    for (int r = lane; r < rows; r += 32)
+                        bulk_load(st.in + r * a.D, usrc + (int64_t)r * a.ss, (uint32_t)a.D * 2u, &s.full[stg]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    const int lane = tid & 31;
+    uint32_t cnt[1 << N];
+#pragma unroll
+    for (int v = 0; v < (1 << N); ++v) cnt[v] = 0;
+    uint32_t it = 0;
+    int running = 0;
+    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        for (int u = 0; u < upt; ++u, ++it) {
+            const int stg = it % kStages;
+            mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status);
+            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], a.left, running, cnt);
+        }
+    }
+    if (HIST) {
+#pragma unroll
+        for (int v = 1; v < (1 << N); ++v) {
+            const uint32_t sum = __reduce_add_sync(kFull, cnt[v]);
+            const int bin = a.left + v;
+            if (lane == 0 && sum != 0 && bin >= 0 && bin < 256) atomicAdd(&s.hist[bin], (int)sum);
+        }
+        consumer_sync();
+        if (tid < 256) {
+            const int hv = s.hist[tid];
+            if (hv != 0) atomicAdd(a.hist + tid, hv);
+        }
+    }
+    bulk_wait_all();
+    __threadfence();
+    consumer_sync();
+    if (tid == 0) {
+        const unsigned ticket = atomicAdd(a.done, 1u);
+        s.is_last = (ticket == gridDim.x - 1);
+    }
+    consumer_sync();
+    if (!s.is_last) return;
+    __threadfence();
+    scan_tile_counts(a, &s.carry, s.scan);
+}
+
+// Gather every unit's escape bytes from its scratch slot into the compact per-segment stream.
+// Tile t of segment j starts at seg_off[j] + tile_base[t] - count[t]; its units follow each other.
+// With `hist` set, the escaped exponents are also counted here (full warps of escape bytes, one
+// shared-memory bin array per warp) rather than one by one inside the pack kernel.
+__global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__restrict__ scratch,
+                                                             const int32_t *__restrict__ tile_counts,
+                                                             const int32_t *__restrict__ unit_counts,
+                                                             const int32_t *__restrict__ tile_base,
+                                                             const int64_t *__restrict__ seg_off, int64_t n_tiles,
+                                                             int BH, int tile_elems, int unit_elems, int upt,
+                                                             uint8_t *__restrict__ escapes, int64_t capacity,
+                                                             int32_t *__restrict__ hist, int32_t *status) {
+    __shared__ int s_hist[kWarps][256];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (hist) {
+        for (int i = tid; i < kWarps * 256; i += kThreads) (&s_hist[0][0])[i] = 0;
+        __syncthreads();
+    }
+    const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t n_warps = (int64_t)gridDim.x * kWarps;
+    for (int64_t t = warp_global; t < n_tiles; t += n_warps) {
+        const int c = tile_counts[t];
+        if (c == 0) continue;
+        int64_t dst = seg_off[t / BH] + tile_base[t] - c;
+        const bool fits = dst >= 0 && dst + c <= capacity;
+        if (!fits && lane == 0) atomicOr(status, ADACODE_STATUS_ESCAPE_OVERFLOW);
+        for (int u = 0; u < upt; ++u) {
+            const int cu = unit_counts[t * upt + u];
+            const uint8_t *src = scratch + t * tile_elems + (int64_t)u * unit_elems;
+            for (int i = lane; i < cu; i += 32) {
+                const uint8_t e = src[i];
+                if (fits) escapes[dst + i] = e;
+                if (hist) atomicAdd(&s_hist[warp][e], 1);
+            }
+            dst += cu;
+        }
+    }
+    if (hist) {
+        __syncthreads();
+        int total = 0;
+#pragma unroll
+        for (int i = 0; i < kWarps; ++i) total += s_hist[i][tid];
+        if (total != 0) atomicAdd(hist + tid, total);
+    }
 }

@@ -213,6 +213,9 @@ class float11Layer(DynamicLayer):
         self._cache_view_runtime: Optional[dict] = None
         self._compressed_prefix_ready_event = None
         self._compressed_prefix_ready_event_pending = False
+        # optional callable applied to every histogram before the adjuster reads it (sharded caches
+        # sum the histograms of all shards here)
+        self.hist_reduce = None
 
     # ------------------------------------------------------------------ reference-named views
     @property
@@ -245,6 +248,7 @@ class float11Layer(DynamicLayer):
         state['_compressed_prefix_ready_event_pending'] = False
         state['_tables'] = {}              # hold raw device addresses
         state['_workspace'] = None
+        state['hist_reduce'] = None          # process groups do not pickle
         state['_mirror'] = {}
         state['_mirror_valid'] = {'k': 0, 'v': 0}
         state['_cache_view_static'] = None
@@ -441,6 +445,9 @@ class float11Layer(DynamicLayer):
         staged block's windows when a block is staged, otherwise it waits in ``new_*``."""
         if keys_exp_count is None or values_exp_count is None:
             return False
+        if self.hist_reduce is not None:
+            keys_exp_count = self.hist_reduce(keys_exp_count)
+            values_exp_count = self.hist_reduce(values_exp_count)
         new_keys = codec.analysis_best_bits(keys_exp_count.to('cpu'))
         new_values = codec.analysis_best_bits(values_exp_count.to('cpu'))
         if not self.compress_params_initialized:
@@ -778,7 +785,8 @@ class float11Layer(DynamicLayer):
 class Float11Cache(Cache):
     """HF ``Cache`` whose layers are ``float11Layer`` (reference: float_cache_utils.py:1556-1814).
 
-    ``dense_workspace`` is the one argument the reference does not have: ``'shared'`` (default)
+    ``hist_reduce`` (optional callable, e.g. ``sharding.HistogramAllReduce``) and
+    ``dense_workspace`` are the arguments the reference does not have.  ``dense_workspace``: ``'shared'`` (default)
     unpacks each layer into one workspace shared by all layers, so the K/V returned by
     ``update`` are valid until the next layer's ``update``; ``'layer'`` keeps an append-only
     dense mirror per layer, as the reference effectively does.
@@ -797,6 +805,7 @@ class Float11Cache(Cache):
         seq_tile_size: Optional[int] = None,
         auto_init_compress_params: bool = False,
         dense_workspace: str = 'shared',
+        hist_reduce=None,
     ):
         config = config.get_text_config(decoder=True)
         auto_init_compress_params = bool(auto_init_compress_params)
@@ -815,6 +824,8 @@ class Float11Cache(Cache):
         else:
             layers = [float11Layer(right[i][0], right[i][1], exp_bits[i][0], exp_bits[i][1], **common)
                       for i in range(n_layers)]
+        for layer in layers:
+            layer.hist_reduce = hist_reduce
         self._init_adjust_schedule(need_adjust, update_steps, block_size, layout)
         self.peak_mem = 0
         self.layout = layout

@@ -307,6 +307,7 @@ class MLAFloat11Cache(Float11Cache):
         validate_shapes: bool = True,
         compress_rope: bool = True,
         dense_workspace: str = 'shared',
+        hist_reduce=None,
     ):
         text_config = config.get_text_config(decoder=True)
         self.mla_cache_mode = str(mla_cache_mode)
@@ -331,7 +332,8 @@ class MLAFloat11Cache(Float11Cache):
         if self.compress_rope:
             super().__init__(config=config, right=self.rights, exp_bits=self.nbits, need_adjust=need_adjust,
                              update_steps=update_steps, residual_length=residual_length, block_size=block_size,
-                             layout=layout, seq_tile_size=seq_tile_size, dense_workspace=dense_workspace)
+                             layout=layout, seq_tile_size=seq_tile_size, dense_workspace=dense_workspace,
+                             hist_reduce=hist_reduce)
             return
         layers = [
             MLALatentFloat11DenseRopeLayer(
@@ -339,6 +341,8 @@ class MLAFloat11Cache(Float11Cache):
                 residual_length=residual_length, block_size=block_size, layout=layout,
                 seq_tile_size=seq_tile_size, dense_workspace=dense_workspace)
             for i in range(num_layers)]
+        for layer in layers:
+            layer.hist_reduce = hist_reduce
         self._init_adjust_schedule(need_adjust, update_steps, block_size, layout)
         self.peak_mem = 0
         self.layout = layout
@@ -399,6 +403,8 @@ class MLAFloat11Cache(Float11Cache):
                 self._take_pending(layer_idx)
             # the reference hands this to a thread pool and reads it at the layer's next update;
             # computed here, delivered at the same point
+            if layer.hist_reduce is not None:
+                keys_exp_count = layer.hist_reduce(keys_exp_count)
             try:
                 self._pending_adjusts[layer_idx] = ('ok', codec.analysis_best_bits(keys_exp_count.to('cpu')))
             except IndexError as exc:
