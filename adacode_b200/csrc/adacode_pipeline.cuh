@@ -144,6 +144,7 @@ struct alignas(128) UnpackStage {
 struct alignas(128) UnpackSmem {
     UnpackStage stage[kStages];
     alignas(128) uint16_t out[kUnitElems];
+    alignas(16) uint32_t lut[1024];   // decode table of the current (left, nbits)
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
     int warp_tot[kPWarps];
@@ -207,17 +208,61 @@ __device__ __forceinline__ TileSrc resolve_tile(const UnpackPipeArgs &a, long lo
     return t;
 }
 
+// ---- table-driven decode -------------------------------------------------------------------
+// The integer pipe (half the rate of the issue slots) is what limits these kernels, so the
+// per-element shifts, masks and adds of the decode are replaced by one shared-memory lookup per
+// pair (or quadruple, or octet) of codes: the table maps a run of packed code bits to the
+// finished exponent fields of the corresponding bf16 pairs, `(e0 << 7) | (e1 << 23)`, with the
+// window's left edge already added.  Index width: 8 bits for N = 1, 2, 4; 6 bits for N = 3.
+template <int N>
+struct DecodeLut {
+    static constexpr int index_bits = (N == 3) ? 6 : 8;
+    static constexpr int elems = index_bits / N;          // elements covered by one lookup
+    static constexpr int words = elems / 2;               // 32-bit pair words per entry
+    static constexpr int entries = 1 << index_bits;
+};
+
+__device__ __forceinline__ void build_decode_lut(uint32_t *lut, int N, int left) {
+    const int index_bits = (N == 3) ? 6 : 8;
+    const int words = (index_bits / N) / 2;
+    const int total = (1 << index_bits) * words;
+    const uint32_t mask = (1u << N) - 1u;
+    for (int w = threadIdx.x; w < total; w += kConsumerThreads) {
+        const uint32_t e = (uint32_t)(w / words), p = (uint32_t)(w % words);
+        const uint32_t c_even = (e >> (index_bits - (2 * p + 1) * N)) & mask;
+        const uint32_t c_odd = (e >> (index_bits - (2 * p + 2) * N)) & mask;
+        lut[w] = (((c_even + (uint32_t)left) & 0xFFu) << 7) | (((c_odd + (uint32_t)left) & 0xFFu) << 23);
+    }
+}
+
+// Exponent fields of the four bf16 pairs of group word g (element 0 in the most significant bits).
+template <int N>
+__device__ __forceinline__ void decode_group(const uint32_t *lut, uint32_t g, uint32_t (&ew)[4]) {
+    if constexpr (N == 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ew[i] = lut[(g >> (24 - 8 * i)) & 0xFFu];
+    } else if constexpr (N == 3) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ew[i] = lut[(g >> (18 - 6 * i)) & 0x3Fu];
+    } else if constexpr (N == 2) {
+        const uint2 hi = reinterpret_cast<const uint2 *>(lut)[(g >> 8) & 0xFFu];
+        const uint2 lo = reinterpret_cast<const uint2 *>(lut)[g & 0xFFu];
+        ew[0] = hi.x, ew[1] = hi.y, ew[2] = lo.x, ew[3] = lo.y;
+    } else {
+        const uint4 v = reinterpret_cast<const uint4 *>(lut)[g & 0xFFu];
+        ew[0] = v.x, ew[1] = v.y, ew[2] = v.z, ew[3] = v.w;
+    }
+}
+
 template <int N>
 __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
-                                            long long &consumed, bool rows_contig, int D, long long ds,
+                                            int &consumed, bool rows_contig, int D, long long ds,
                                             int32_t *status) {
     constexpr int CB = 2 * N;   // code bytes per 16-element chunk
-    constexpr uint32_t kMask = (1u << N) - 1u;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const UnitMeta m = st.meta;
     if (m.first_unit_of_tile) consumed = 0;
     const int chunks = m.elems >> 4;
-    const uint32_t left2 = ((uint32_t)m.left & 0xFFu) * 0x10001u;
 
     uint4 o[kPCPT][2];
     uint32_t zm[kPCPT][2];
@@ -238,14 +283,14 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
         for (int q = 0; q < 2; ++q) {
             zm[k][q] = valid ? zero_slots<N>(g[q]) : 0u;
             zc[k] += __popc(zm[k][q]);
-            uint32_t cd[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) cd[j] = (g[q] >> ((7 - j) * N)) & kMask;
+            uint32_t ew[4];
+            decode_group<N>(s.lut, g[q], ew);
             const uint32_t s0 = sw[2 * q], s1 = sw[2 * q + 1];
-            o[k][q].x = assemble2(__byte_perm(s0, 0u, 0x4140), cd[0], cd[1], left2);
-            o[k][q].y = assemble2(__byte_perm(s0, 0u, 0x4342), cd[2], cd[3], left2);
-            o[k][q].z = assemble2(__byte_perm(s1, 0u, 0x4140), cd[4], cd[5], left2);
-            o[k][q].w = assemble2(__byte_perm(s1, 0u, 0x4342), cd[6], cd[7], left2);
+            // sign and mantissa: each byte doubled into its 16-bit lane, then masked into place
+            o[k][q].x = ew[0] | (__byte_perm(s0, 0u, 0x1100) & 0x807F807Fu);
+            o[k][q].y = ew[1] | (__byte_perm(s0, 0u, 0x3322) & 0x807F807Fu);
+            o[k][q].z = ew[2] | (__byte_perm(s1, 0u, 0x1100) & 0x807F807Fu);
+            o[k][q].w = ew[3] | (__byte_perm(s1, 0u, 0x3322) & 0x807F807Fu);
         }
     }
     int incl[kPCPT];
@@ -264,29 +309,39 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     for (int k = 0; k < kPCPT; ++k) {
         const int c = warp * (kPCPT * 32) + k * 32 + lane;
         if (c < chunks) {
-            uint4 *w = reinterpret_cast<uint4 *>(s.out + c * 16);
-            w[0] = o[k][0];
-            w[1] = o[k][1];
+            uint16_t *ow = s.out + c * 16;
+            reinterpret_cast<uint4 *>(ow)[0] = o[k][0];
+            reinterpret_cast<uint4 *>(ow)[1] = o[k][1];
             if (zc[k] != 0) {
-                long long r = consumed + wprefix + incl[k] - zc[k];
+                int r = consumed + wprefix + incl[k] - zc[k];     // rank inside the tile
+                if (r + zc[k] <= m.esc_staged) {
+                    const uint8_t *ep = st.esc + m.esc_shift + r;
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint32_t z = zm[k][q];
-                    while (z) {
-                        const int pos = 31 - __clz(z);
-                        z ^= 1u << pos;
-                        const int el = q * 8 + 7 - pos / N;
-                        uint32_t e = 0;
-                        if (r < m.esc_staged) {
-                            e = st.esc[m.esc_shift + (int)r];
-                        } else if (m.esc_tile_start + r < m.esc_len) {
-                            e = m.esc[m.esc_tile_start + r];
-                        } else {
-                            atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
+                    for (int q = 0; q < 2; ++q) {
+                        uint32_t z = zm[k][q];
+                        while (z) {
+                            const int pos = 31 - __clz(z);
+                            z ^= 1u << pos;
+                            uint16_t *pw = ow + (q * 8 + 7 - pos / N);
+                            *pw = (uint16_t)((*pw & 0x807Fu) | ((uint32_t)(*ep++) << 7));
                         }
-                        ++r;
-                        uint16_t *pw = s.out + c * 16 + el;
-                        *pw = (uint16_t)((*pw & 0x807Fu) | (e << 7));
+                    }
+                } else {
+                    // beyond the staged window (or beyond the stream): fetch from global memory
+#pragma unroll 1
+                    for (int q = 0; q < 2; ++q) {
+                        uint32_t z = zm[k][q];
+                        while (z) {
+                            const int pos = 31 - __clz(z);
+                            z ^= 1u << pos;
+                            uint32_t e = 0;
+                            if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
+                            else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
+                            else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
+                            ++r;
+                            uint16_t *pw = ow + (q * 8 + 7 - pos / N);
+                            *pw = (uint16_t)((*pw & 0x807Fu) | (e << 7));
+                        }
                     }
                 }
             }
@@ -389,13 +444,23 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
 
     // ---------------- consumer warps ----------------
     uint32_t it = 0;
-    long long consumed = 0;
+    int consumed = 0;
+    int lut_left = 0, lut_nbits = 0;      // what s.lut currently encodes (nbits 0: nothing yet)
     for (long long tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
         for (int u = 0; u < units_per_tile; ++u, ++it) {
             const int stg = it % kStages;
-            mbar_wait(&s.full[stg], (it / kStages) & 1, a.status);
+            if ((tid & 31) == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, a.status);
+            __syncwarp();
             const UnpackStage &st = s.stage[stg];
-            switch (st.meta.nbits) {
+            const int nb = st.meta.nbits, lf = st.meta.left;
+            if (nb != lut_nbits || lf != lut_left) {
+                // uniform over the CTA: every consumer read the same meta.  The previous unit ended
+                // with a consumer barrier, so nobody still reads the old table.
+                build_decode_lut(s.lut, nb, lf);
+                lut_nbits = nb, lut_left = lf;
+                consumer_sync();
+            }
+            switch (nb) {
                 case 1: unpack_unit<1>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
                 case 2: unpack_unit<2>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
                 case 3: unpack_unit<3>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
@@ -476,6 +541,7 @@ struct alignas(128) PackSmem {
     alignas(128) uint8_t sm[kUnitElems];
     alignas(128) uint8_t codes[kUnitElems / 2];
     alignas(128) uint8_t esc[kPackEscStage];
+    alignas(16) uint8_t lut[256];      // exponent -> code (0 = outside the window)
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
     int warp_tot[kPWarps];
@@ -558,16 +624,29 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
             w0 = p[0];
             w1 = p[1];
         }
-        const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wb[4] = {w1.x, w1.y, w1.z, w1.w};
-        g[2 * k] = valid ? encode_group<N>(wa, left) : 0u;
-        g[2 * k + 1] = valid ? encode_group<N>(wb, left) : 0u;
-        zm[k][0] = valid ? zero_slots<N>(g[2 * k]) : 0u;
-        zm[k][1] = valid ? zero_slots<N>(g[2 * k + 1]) : 0u;
+        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint32_t smw[4];
+        uint32_t gg[2] = {0u, 0u};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            // four elements: their low bytes [e0 m6..m0] and high bytes [s e7..e1]
+            const uint32_t lo4 = __byte_perm(w[2 * q], w[2 * q + 1], 0x6420);
+            const uint32_t hi4 = __byte_perm(w[2 * q], w[2 * q + 1], 0x7531);
+            smw[q] = (hi4 & 0x80808080u) | (lo4 & 0x7F7F7F7Fu);
+            const uint32_t e4 = ((hi4 & 0x7F7F7F7Fu) << 1) | ((lo4 >> 7) & 0x01010101u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t code = s.lut[(e4 >> (8 * j)) & 0xFFu];     // 0 when out of the window
+                const int el = 4 * q + j;
+                gg[el >> 3] = code * (1u << ((7 - (el & 7)) * N)) + gg[el >> 3];
+            }
+        }
+        g[2 * k] = valid ? gg[0] : 0u;
+        g[2 * k + 1] = valid ? gg[1] : 0u;
+        zm[k][0] = valid ? zero_slots<N>(gg[0]) : 0u;
+        zm[k][1] = valid ? zero_slots<N>(gg[1]) : 0u;
         zc[k] = __popc(zm[k][0]) + __popc(zm[k][1]);
-        smv[k].x = signmant4(w0.x, w0.y);
-        smv[k].y = signmant4(w0.z, w0.w);
-        smv[k].z = signmant4(w1.x, w1.y);
-        smv[k].w = signmant4(w1.z, w1.w);
+        smv[k] = make_uint4(smw[0], smw[1], smw[2], smw[3]);
     }
     if (HIST) count_codes_overlaid<N, kPCPT * 2>(g, cnt);
 
@@ -637,6 +716,10 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (HIST && tid < 256) s.hist[tid] = 0;
+    if (tid < 256) {
+        const uint32_t code = (uint32_t)tid - (uint32_t)a.left;
+        s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
+    }
     __syncthreads();
 
     const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
@@ -694,7 +777,8 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
     for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
         for (int u = 0; u < upt; ++u, ++it) {
             const int stg = it % kStages;
-            mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status);
+            if (lane == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status);
+            __syncwarp();
             pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], a.left, running, cnt);
         }
     }
