@@ -963,7 +963,8 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
     const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 8
                                 ? (n_tiles + kWarps - 1) / kWarps
                                 : (int64_t)sm_count() * 8);
-    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D)) {
+    // (the pipelined kernel counts histogram hits in 16-bit fields per thread: keep tiles below 2**24 elements)
+    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D) && tile_elems <= (1 << 24)) {
         PackPipeArgs pa;
         pa.base = a;
         pa.unit_counts = unit_counts;

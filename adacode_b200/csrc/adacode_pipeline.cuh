@@ -106,6 +106,23 @@ __device__ __forceinline__ int warp_scan_counts(const int (&cnt)[kPCPT], int (&i
     return total;
 }
 
+// Exclusive prefix of this warp and the total over all consumer warps, from the per-warp totals
+// in shared memory: lane i reads warp i's total, one warp scan, two shuffles.
+__device__ __forceinline__ void cross_warp_prefix(const int *warp_tot, int &prefix, int &total) {
+    static_assert(kPWarps <= 32, "one lane per consumer warp");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int x = lane < kPWarps ? warp_tot[lane] : 0;
+#pragma unroll
+    for (int d = 1; d < kPWarps; d <<= 1) {
+        const int u = __shfl_up_sync(kFull, x, d);
+        if (lane >= d) x += u;
+    }
+    total = __shfl_sync(kFull, x, kPWarps - 1);
+    const int incl = __shfl_sync(kFull, x, warp);
+    const int own = __shfl_sync(kFull, lane < kPWarps ? warp_tot[lane] : 0, warp);
+    prefix = incl - own;
+}
+
 // Rows of one tile handled per unit: whole rows, a multiple of 8 (so that code bytes per unit are a
 // multiple of 16), at most kUnitElems elements.
 __host__ __device__ inline int unit_rows_for(int seq_tile, int D) {
@@ -298,13 +315,8 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     if (lane == 0) s.warp_tot[warp] = wtot;
     bulk_wait_read();          // the previous unit's store has finished reading s.out
     consumer_sync();
-    int wprefix = 0, unit_tot = 0;
-#pragma unroll
-    for (int i = 0; i < kPWarps; ++i) {
-        const int t = s.warp_tot[i];
-        wprefix += (i < warp) ? t : 0;
-        unit_tot += t;
-    }
+    int wprefix, unit_tot;
+    cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = warp * (kPCPT * 32) + k * 32 + lane;
@@ -489,8 +501,13 @@ __device__ __forceinline__ uint32_t overlay_shift(int j) {
     return (uint32_t)(8 * j);                                 // N == 1: one byte per group
 }
 
+// Counters live in registers, two 16-bit fields per register: a thread sees fewer than 2**31 /
+// (CTAs x threads) elements in one launch, far below 65536 per code value.
+template <int N>
+struct HistRegs { static constexpr int v = (1 << N) / 2 > 0 ? (1 << N) / 2 : 1; };
+
 template <int N, int NG>
-__device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], uint32_t (&cnt)[1 << N]) {
+__device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], uint32_t (&cnt2)[HistRegs<N>::v]) {
     constexpr int GPW = GroupsPerWord<N>::v;
     constexpr uint32_t M = SlotLsb<N>::v;
 #pragma unroll
@@ -505,7 +522,7 @@ __device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], ui
                 const uint32_t sh = overlay_shift<N>(j);
                 used |= M << sh;
 #pragma unroll
-                for (int i = 0; i < N; ++i) plane[i] |= ((g[base + j] >> i) & M) << sh;
+                for (int i = 0; i < N; ++i) plane[i] = ((g[base + j] >> i) & M) * (1u << sh) + plane[i];
             }
         }
 #pragma unroll
@@ -513,7 +530,7 @@ __device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], ui
             uint32_t m = used;
 #pragma unroll
             for (int i = 0; i < N; ++i) m &= ((v >> i) & 1) ? plane[i] : ~plane[i];
-            cnt[v] += __popc(m);
+            cnt2[v >> 1] = (uint32_t)__popc(m) * ((v & 1) ? 65536u : 1u) + cnt2[v >> 1];
         }
     }
 }
@@ -604,7 +621,7 @@ __device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s
 
 template <int N, bool HIST>
 __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint64_t *empty_bar, int left,
-                                          int &running, uint32_t (&cnt)[1 << N]) {
+                                          int &running, uint32_t (&cnt2)[HistRegs<N>::v]) {
     constexpr int CB = 2 * N;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const PackUnitMeta m = st.meta;
@@ -648,20 +665,15 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
         zc[k] = __popc(zm[k][0]) + __popc(zm[k][1]);
         smv[k] = make_uint4(smw[0], smw[1], smw[2], smw[3]);
     }
-    if (HIST) count_codes_overlaid<N, kPCPT * 2>(g, cnt);
+    if (HIST) count_codes_overlaid<N, kPCPT * 2>(g, cnt2);
 
     int incl[kPCPT];
     const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;
     bulk_wait_read();      // the previous unit's stores have finished reading the out buffers
     consumer_sync();
-    int wprefix = 0, unit_tot = 0;
-#pragma unroll
-    for (int i = 0; i < kPWarps; ++i) {
-        const int t = s.warp_tot[i];
-        wprefix += (i < warp) ? t : 0;
-        unit_tot += t;
-    }
+    int wprefix, unit_tot;
+    cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = warp * (kPCPT * 32) + k * 32 + lane;
@@ -769,9 +781,9 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
 
     // ---------------- consumer warps ----------------
     const int lane = tid & 31;
-    uint32_t cnt[1 << N];
+    uint32_t cnt2[HistRegs<N>::v];
 #pragma unroll
-    for (int v = 0; v < (1 << N); ++v) cnt[v] = 0;
+    for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
     uint32_t it = 0;
     int running = 0;
     for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
@@ -779,13 +791,14 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
             const int stg = it % kStages;
             if (lane == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status);
             __syncwarp();
-            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], a.left, running, cnt);
+            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], a.left, running, cnt2);
         }
     }
     if (HIST) {
 #pragma unroll
         for (int v = 1; v < (1 << N); ++v) {
-            const uint32_t sum = __reduce_add_sync(kFull, cnt[v]);
+            const uint32_t mine = (cnt2[v >> 1] >> (16 * (v & 1))) & 0xFFFFu;
+            const uint32_t sum = __reduce_add_sync(kFull, mine);
             const int bin = a.left + v;
             if (lane == 0 && sum != 0 && bin >= 0 && bin < 256) atomicAdd(&s.hist[bin], (int)sum);
         }
