@@ -833,12 +833,15 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
                                                              int BH, int tile_elems, int unit_elems, int upt,
                                                              uint8_t *__restrict__ escapes, int64_t capacity,
                                                              int32_t *__restrict__ hist, int32_t *status) {
-    __shared__ int s_hist[kWarps][256];
+    // per warp four copies of the 256 bins (picked by lane & 3): escaped exponents cluster on a few
+    // values, so one copy would serialise most of a warp's shared atomics
+    __shared__ int s_hist[kWarps][4][256];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (hist) {
-        for (int i = tid; i < kWarps * 256; i += kThreads) (&s_hist[0][0])[i] = 0;
+        for (int i = tid; i < kWarps * 4 * 256; i += kThreads) (&s_hist[0][0][0])[i] = 0;
         __syncthreads();
     }
+    int *my_hist = &s_hist[warp][lane & 3][0];
     const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t n_warps = (int64_t)gridDim.x * kWarps;
     for (int64_t t = warp_global; t < n_tiles; t += n_warps) {
@@ -849,11 +852,19 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
         if (!fits && lane == 0) atomicOr(status, ADACODE_STATUS_ESCAPE_OVERFLOW);
         for (int u = 0; u < upt; ++u) {
             const int cu = unit_counts[t * upt + u];
-            const uint8_t *src = scratch + t * tile_elems + (int64_t)u * unit_elems;
-            for (int i = lane; i < cu; i += 32) {
-                const uint8_t e = src[i];
-                if (fits) escapes[dst + i] = e;
-                if (hist) atomicAdd(&s_hist[warp][e], 1);
+            // unit slots start on 16-byte boundaries: read four escape bytes per lane and step
+            const uint32_t *src4 = reinterpret_cast<const uint32_t *>(scratch + t * tile_elems + (int64_t)u * unit_elems);
+            for (int i = lane * 4; i < cu; i += 128) {
+                uint32_t v = src4[i >> 2];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (i + b < cu) {
+                        const uint32_t e = v & 0xFFu;
+                        if (fits) escapes[dst + i + b] = (uint8_t)e;
+                        if (hist) atomicAdd(my_hist + e, 1);
+                    }
+                    v >>= 8;
+                }
             }
             dst += cu;
         }
@@ -862,7 +873,8 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
         __syncthreads();
         int total = 0;
 #pragma unroll
-        for (int i = 0; i < kWarps; ++i) total += s_hist[i][tid];
+        for (int i = 0; i < kWarps; ++i)
+            total += s_hist[i][0][tid] + s_hist[i][1][tid] + s_hist[i][2][tid] + s_hist[i][3][tid];
         if (total != 0) atomicAdd(hist + tid, total);
     }
 }
