@@ -17,6 +17,7 @@ ERR_CUDA = -2
 ERR_WORKSPACE = -3
 ERR_NO_CANDIDATE = -4
 ERR_TOO_LARGE = -5
+STATIC_SCRATCH_BYTES = 4 * 1024 * 1024 + 512 * 1024
 STATUS_ESCAPE_OVERFLOW = 1
 STATUS_ESCAPE_UNDERRUN = 2
 
@@ -24,7 +25,7 @@ STATUS_ESCAPE_UNDERRUN = 2
 EXPORTED_SYMBOLS = (
     'adacode_version', 'adacode_strerror', 'adacode_last_cuda_error', 'adacode_pack_workspace_bytes',
     'adacode_pack_tiles', 'adacode_unpack_tiles', 'adacode_unpack_segments', 'adacode_hist_bf16',
-    'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host',
+    'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host', 'adacode_pack_tiles_static',
 )
 
 
@@ -64,6 +65,9 @@ def lib() -> ctypes.CDLL:
     L.adacode_pack_tiles.restype = i32
     L.adacode_pack_tiles.argtypes = [vp, i64, i64, i64, i32, i32, i32, i32, i32, i32, i32,
                                      vp, vp, vp, i64, vp, vp, vp, vp, sz, vp, vp]
+    L.adacode_pack_tiles_static.restype = i32
+    L.adacode_pack_tiles_static.argtypes = [vp, i64, i64, i64, i32, i32, i32, i32, i32, i32, i32,
+                                            vp, vp, vp, i64, vp, vp, vp, vp, vp]
     L.adacode_unpack_tiles.restype = i32
     L.adacode_unpack_tiles.argtypes = [vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                        vp, i64, i64, i64, vp, vp]

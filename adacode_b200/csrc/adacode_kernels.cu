@@ -1121,3 +1121,45 @@ int adacode_calibrate_host(const int64_t *hist256, int *right, int *nbits) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// pack without a caller-provided scratch
+// ---------------------------------------------------------------------------------------
+
+// Library-owned pack scratch.  In host code this name is only a handle for the runtime's symbol
+// lookup, not a device address: the address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_static_pack_scratch[ADACODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int adacode_pack_tiles_static(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                                         int B, int H, int n_blocks, int seq_tile, int D, int right, int nbits,
+                                         uint8_t *sign_mant, uint8_t *codes, uint8_t *escapes,
+                                         int64_t escapes_capacity, int32_t *tile_base, int64_t *seg_escape_offsets,
+                                         int32_t *hist256, int32_t *status, void *stream) {
+    if (B < 0 || H < 0 || n_blocks < 0 || seq_tile <= 0 || D <= 0) return ADACODE_ERR_INVALID_ARG;
+    const int64_t n_tiles = (int64_t)B * H * n_blocks;
+    const int64_t tile_elems = (int64_t)seq_tile * D;
+    if (n_tiles > 0 && adacode_pack_workspace_bytes(n_tiles, tile_elems) > (size_t)ADACODE_STATIC_SCRATCH_BYTES)
+        return ADACODE_ERR_WORKSPACE;   // larger than the built-in scratch: nothing was launched
+    int dev = 0;
+    ADACODE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return ADACODE_ERR_INVALID_ARG;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device (it is the current one): resolve the device address of the array
+        void *addr = nullptr;
+        ADACODE_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_pack_scratch));
+        if (addr == nullptr) return ADACODE_ERR_CUDA;
+        g_static_scratch_addr[dev] = addr;
+    }
+    void *scratch = g_static_scratch_addr[dev];
+    // the completion counter at the head of the scratch must be zero when the kernel starts;
+    // whatever an earlier (possibly failed) call left there is cleared in stream order
+    ADACODE_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, (cudaStream_t)stream));
+    return adacode_pack_tiles(src_bf16, stride_b, stride_h, stride_s, B, H, n_blocks, seq_tile, D, right, nbits,
+                              sign_mant, codes, escapes, escapes_capacity, tile_base, seg_escape_offsets, hist256,
+                              scratch, (size_t)ADACODE_STATIC_SCRATCH_BYTES, status, stream);
+}

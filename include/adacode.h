@@ -94,6 +94,42 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
                        void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
+ * Maximum size of the library-owned scratch used by adacode_pack_tiles_static, in bytes.
+ * A call fits when adacode_pack_workspace_bytes(n_tiles, tile_elems) is not larger (roughly
+ * 4 Mi bf16 elements per call, e.g. thirty-two 128-token blocks of an [8, 128]-shaped head set).
+ */
+#define ADACODE_STATIC_SCRATCH_BYTES (4u * 1024u * 1024u + 512u * 1024u)
+
+/*
+ * adacode_pack_tiles for callers that cannot allocate device memory.
+ * This entry point has no counterpart in the reference implementation.
+ *
+ * Some hosts of this library own no allocator at the moment they need to pack: a serving
+ * process that carved up the whole GPU at start-up and treats every later cudaMalloc as a
+ * fault (it stalls all streams of the device), or a plain C program that binds this library
+ * without a tensor framework behind it.  For them the pack scratch (escape slots, per-tile
+ * counts and the completion counter that the caller of adacode_pack_tiles must provide) lives
+ * in a file-scope __device__ array of ADACODE_STATIC_SCRATCH_BYTES inside the library; every
+ * GPU that loads the library holds that array until the process exits.  Inputs and outputs
+ * are still the caller's.  Nothing is allocated or freed by this call.
+ *
+ * Limits and rules:
+ *   - a call whose scratch need exceeds ADACODE_STATIC_SCRATCH_BYTES is rejected with
+ *     ADACODE_ERR_WORKSPACE and does nothing; split the span into fewer blocks per call;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - all calls on a device share the one array, which keeps what the previous call left:
+ *     the call clears the part that must start at zero itself, on `stream`, but two calls
+ *     whose kernels overlap on the GPU (different streams, no ordering) race on it.
+ * Arguments and results are those of adacode_pack_tiles without workspace/workspace_bytes.
+ */
+int adacode_pack_tiles_static(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                              int B, int H, int n_blocks, int seq_tile, int D, int right, int nbits,
+                              uint8_t *sign_mant, uint8_t *codes, uint8_t *escapes, int64_t escapes_capacity,
+                              int32_t *tile_base, int64_t *seg_escape_offsets, int32_t *hist256,
+                              int32_t *status, void *stream);
+
+/*
  * Inverse of adacode_pack_tiles for planes laid out as that call writes them.
  * Replaces: TiledCompressedTensor.materialize / materialize_tiled_state /
  *   _decode_tiled_bf16_kernel (compress_tiled_kv.py:313-337, :754-791, :33-93),
