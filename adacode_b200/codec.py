@@ -150,6 +150,66 @@ class TiledCompressedTensor:
         return out
 
 
+class SegmentRef:
+    """Handle on segment ``j`` of a ``PackedChunk``: everything the cache's bookkeeping needs
+    (window, shape, escape count, byte accounting) is arithmetic on the chunk, so a prefill of
+    hundreds of blocks creates no per-block tensor views; ``view()`` materialises the reference-
+    shaped ``TiledCompressedTensor`` on demand."""
+
+    __slots__ = ('chunk', 'j')
+
+    def __init__(self, chunk: 'PackedChunk', j: int):
+        self.chunk = chunk
+        self.j = int(j)
+
+    left = property(lambda self: self.chunk.left)
+    right = property(lambda self: self.chunk.right)
+    nbits = property(lambda self: self.chunk.nbits)
+    seq_tile_size = property(lambda self: self.chunk.seq_tile)
+    head_dim = property(lambda self: self.chunk.head_dim)
+
+    @property
+    def original_shape(self) -> tuple:
+        c = self.chunk
+        return (c.batch, c.heads, c.seq_tile, c.head_dim)
+
+    @property
+    def n_elements(self) -> int:
+        c = self.chunk
+        return c.batch * c.heads * c.seq_tile * c.head_dim
+
+    @property
+    def n_escapes(self) -> int:
+        off = self.chunk.seg_offsets
+        return int(off[self.j + 1]) - int(off[self.j])
+
+    def view(self) -> TiledCompressedTensor:
+        return self.chunk.segment(self.j)
+
+    # tensor fields, for code written against TiledCompressedTensor
+    sign_mass_data = property(lambda self: self.view().sign_mass_data)
+    exp_data = property(lambda self: self.view().exp_data)
+    invalid_exp = property(lambda self: self.view().invalid_exp)
+    tile_invalid_base = property(lambda self: self.view().tile_invalid_base)
+
+    def get_memory(self) -> dict:
+        """compress_tiled_kv.py:269-282, without touching a tensor."""
+        c = self.chunk
+        n = self.n_elements
+        compressed = n + n * c.nbits // 8 + self.n_escapes + 4 * c.batch * c.heads
+        return {'compressed_memory': compressed, 'original_memory': 2 * n,
+                'ratio': 0.0 if n == 0 else compressed / (2 * n)}
+
+    def export_state(self) -> dict:
+        return self.view().export_state()
+
+    def export_decode_view(self) -> dict:
+        return self.view().export_decode_view()
+
+    def materialize(self) -> torch.Tensor:
+        return self.view().materialize()
+
+
 @dataclass
 class PackedChunk:
     """``n_blocks`` consecutive segments produced by one pack launch with one window.
@@ -194,7 +254,8 @@ class PackedChunk:
         return seg
 
     def segments(self) -> list:
-        return [self.segment(j) for j in range(self.n_blocks)]
+        """Cheap handles, one per block (``SegmentRef``)."""
+        return [SegmentRef(self, j) for j in range(self.n_blocks)]
 
 
 # --------------------------------------------------------------------------------------
@@ -310,30 +371,79 @@ def _check_dst(dst: torch.Tensor, B: int, H: int, D: int, min_seq: int) -> None:
         raise ValueError('dst must have unit stride along head_dim')
 
 
-def build_segment_table(segments: Sequence[TiledCompressedTensor], seq_offsets: Optional[Sequence[int]] = None,
+_SEGMENT_DTYPE = None
+
+
+def _segment_dtype():
+    """numpy mirror of ``struct adacode_segment`` (56 bytes)."""
+    global _SEGMENT_DTYPE
+    if _SEGMENT_DTYPE is None:
+        import numpy as np
+        _SEGMENT_DTYPE = np.dtype([('sign_mant', '<u8'), ('codes', '<u8'), ('escapes', '<u8'), ('tile_base', '<u8'),
+                                   ('escapes_len', '<i8'), ('dst_seq_offset', '<i8'), ('left', '<i4'),
+                                   ('nbits', '<i4')])
+        assert _SEGMENT_DTYPE.itemsize == ctypes.sizeof(_lib.Segment)
+    return _SEGMENT_DTYPE
+
+
+def build_segment_table(segments: Sequence, seq_offsets: Optional[Sequence[int]] = None,
                         device=None) -> torch.Tensor:
     """Device array of ``adacode_segment`` records (as uint8) for ``unpack_segments``.
     ``seq_offsets[i]`` is segment i's first token in the destination; the default stacks the
-    segments one after the other."""
+    segments one after the other.  Runs of ``SegmentRef`` from one chunk are filled with array
+    arithmetic on the chunk's base pointers, so a table over hundreds of blocks costs a handful
+    of numpy operations."""
+    import numpy as np
     n = len(segments)
-    table = (_lib.Segment * max(n, 1))()
-    run = 0
-    for i, seg in enumerate(segments):
-        off = run if seq_offsets is None else int(seq_offsets[i])
-        e = table[i]
-        e.sign_mant = seg.sign_mass_data.data_ptr()
-        e.codes = seg.exp_data.data_ptr()
-        e.escapes = seg.invalid_exp.data_ptr() if seg.invalid_exp.numel() else 0
-        e.tile_base = seg.tile_invalid_base.data_ptr()
-        e.escapes_len = seg.invalid_exp.numel()
-        e.dst_seq_offset = off
-        e.left = int(seg.left)
-        e.nbits = int(seg.nbits)
-        run = off + int(seg.original_shape[-2])
-    raw = bytes(table)[: n * ctypes.sizeof(_lib.Segment)]
-    host = torch.frombuffer(bytearray(raw), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
+    table = np.zeros(max(n, 1), dtype=_segment_dtype())
+    i = 0
+    run_tokens = 0
+    while i < n:
+        seg = segments[i]
+        if isinstance(seg, SegmentRef):
+            c = seg.chunk
+            k = i + 1
+            while k < n and isinstance(segments[k], SegmentRef) and segments[k].chunk is c \
+                    and segments[k].j == segments[k - 1].j + 1:
+                k += 1
+            js = np.arange(seg.j, seg.j + (k - i), dtype=np.int64)
+            offs = np.asarray(c.seg_offsets, dtype=np.int64)
+            bh = c.batch * c.heads
+            tile = c.seq_tile * c.head_dim
+            rows = table[i:k]
+            rows['sign_mant'] = c.sign_mant.data_ptr() + js * (bh * tile)
+            rows['codes'] = c.codes.data_ptr() + js * (bh * tile * c.nbits // 8)
+            esc_base = c.escapes.data_ptr() if c.escapes.numel() else 0
+            lens = offs[js + 1] - offs[js]
+            rows['escapes'] = np.where(lens > 0, esc_base + offs[js], 0)
+            rows['tile_base'] = c.tile_base.data_ptr() + js * (4 * bh)
+            rows['escapes_len'] = lens
+            rows['left'] = c.left
+            rows['nbits'] = c.nbits
+            tokens = np.full(k - i, c.seq_tile, dtype=np.int64)
+        else:
+            k = i + 1
+            rows = table[i:k]
+            rows['sign_mant'] = seg.sign_mass_data.data_ptr()
+            rows['codes'] = seg.exp_data.data_ptr()
+            rows['escapes'] = seg.invalid_exp.data_ptr() if seg.invalid_exp.numel() else 0
+            rows['tile_base'] = seg.tile_invalid_base.data_ptr()
+            rows['escapes_len'] = seg.invalid_exp.numel()
+            rows['left'] = int(seg.left)
+            rows['nbits'] = int(seg.nbits)
+            tokens = np.asarray([int(seg.original_shape[-2])], dtype=np.int64)
+        if seq_offsets is None:
+            starts = run_tokens + np.concatenate(([0], np.cumsum(tokens)[:-1]))
+            run_tokens += int(tokens.sum())
+        else:
+            starts = np.asarray([int(v) for v in seq_offsets[i:k]], dtype=np.int64)
+            run_tokens = int(starts[-1] + tokens[-1])
+        rows['dst_seq_offset'] = starts
+        i = k
+    host = torch.from_numpy(table[:n].view(np.uint8).reshape(-1).copy()) if n else torch.empty(0, dtype=torch.uint8)
     if device is None:
-        device = segments[0].sign_mass_data.device
+        s0 = segments[0]
+        device = s0.chunk.sign_mant.device if isinstance(s0, SegmentRef) else s0.sign_mass_data.device
     return host.to(device, non_blocking=False)
 
 

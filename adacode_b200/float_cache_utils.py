@@ -34,7 +34,7 @@ from transformers import Cache
 from transformers.cache_utils import DynamicLayer
 
 from . import codec
-from .codec import TiledCompressedTensor
+from .codec import SegmentRef, TiledCompressedTensor
 
 _SUPPORTED_LAYOUTS = ('segmented_tiled',)
 
@@ -186,8 +186,8 @@ class float11Layer(DynamicLayer):
         self.prefill_reuse_hits = 0
         self.auto_init_compress_param_updates = 0
         # packed prefix: one entry per 128-token block, for keys and for values
-        self._key_segments: list[TiledCompressedTensor] = []
-        self._value_segments: list[TiledCompressedTensor] = []
+        self._key_segments: list[SegmentRef] = []
+        self._value_segments: list[SegmentRef] = []
         self._compressed_prefix_seq_len = 0
         self._compressed_block_flushes = 0
         self._compressed_tokens_flushed = 0
@@ -654,8 +654,8 @@ class float11Layer(DynamicLayer):
             km, vm = k.get_memory(), v.get_memory()
             compressed += km['compressed_memory'] + vm['compressed_memory']
             original += km['original_memory'] + vm['original_memory']
-            k_ratio += k.invalid_exp.numel() / k.n_elements if k.n_elements else 0.0
-            v_ratio += v.invalid_exp.numel() / v.n_elements if v.n_elements else 0.0
+            k_ratio += k.n_escapes / k.n_elements if k.n_elements else 0.0
+            v_ratio += v.n_escapes / v.n_elements if v.n_elements else 0.0
         res_k, res_v = self._active_residual_tensors()
         if res_k is not None:
             res_bytes = res_k.numel() * res_k.element_size() + res_v.numel() * res_v.element_size()

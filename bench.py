@@ -316,20 +316,46 @@ def run_gpu_arm(args) -> None:
     cfg = StubConfig(LAYERS)
     host_in = [s.x.to('cpu').pin_memory() for s in slots]
     host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(2)]
-    stage = [torch.empty_like(slots[0].x) for _ in range(2)]
     e2e_steps = max(1, min(args.steps, 3))
 
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    stage = [[torch.empty_like(slots[0].x) for _ in range(2)] for _ in range(2)]      # double-buffered K, V
+
     def e2e_step():
+        """Host K/V -> device -> Float11Cache.update (pack) -> materialize_layer (unpack) -> host.
+        The copies of neighbouring layers run on their own streams so that PCIe traffic in both
+        directions overlaps the kernels; per-layer dense mirrors keep a layer's unpacked K/V alive
+        while it is copied out."""
+        main = torch.cuda.current_stream(dev)
         cache = Float11Cache(cfg, right=rights, exp_bits=nbits, need_adjust=True, update_steps=128,
-                             residual_length=0, block_size=BLOCK, layout='segmented_tiled')
+                             residual_length=0, block_size=BLOCK, layout='segmented_tiled', dense_workspace='layer')
+        ready = [torch.cuda.Event() for _ in range(2)]
+        free = [torch.cuda.Event() for _ in range(2)]
+
+        def upload(l):
+            buf = l & 1
+            with torch.cuda.stream(copy_in):
+                if l >= 2:
+                    copy_in.wait_event(free[buf])
+                stage[buf][0].copy_(host_in[2 * l], non_blocking=True)
+                stage[buf][1].copy_(host_in[2 * l + 1], non_blocking=True)
+                ready[buf].record(copy_in)
+
+        upload(0)
         for l in range(LAYERS):
-            stage[0].copy_(host_in[2 * l], non_blocking=True)
-            stage[1].copy_(host_in[2 * l + 1], non_blocking=True)
-            cache.update(stage[0], stage[1], l)
-        for l in range(LAYERS):
+            buf = l & 1
+            if l + 1 < LAYERS:
+                upload(l + 1)
+            main.wait_event(ready[buf])
+            cache.update(stage[buf][0], stage[buf][1], l)
+            free[buf].record(main)
             dk, dv = cache.materialize_layer(l)
-            host_out[0].copy_(dk, non_blocking=True)
-            host_out[1].copy_(dv, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                host_out[0].copy_(dk, non_blocking=True)
+                host_out[1].copy_(dv, non_blocking=True)
         torch.cuda.synchronize(dev)
         return cache
 
