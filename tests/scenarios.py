@@ -195,3 +195,25 @@ def run_scenario(sc: Scenario, make_cache, device='cpu', check_dense: bool = Tru
         assert torch.equal(mk.cpu().view(torch.int16), torch.cat(seen_k[l], dim=-2).view(torch.int16))
         assert torch.equal(mv.cpu().view(torch.int16), torch.cat(seen_v[l], dim=-2).view(torch.int16))
     return digest, cache
+
+
+def stress_scenario(batch=4, heads=8, dim=128, prefill=512, decode=384, layers=2, seed=41):
+    """Reduced replica of the multi-GPU stress configuration: after `prefill` tokens the scale of
+    half the heads doubles, 0.1 % of the values carry exponents outside the calibrated window and
+    0.01 % are zero/subnormal; the prompt is a whole number of blocks and the rest arrives one
+    token at a time, so blocks fill exactly on adjust steps."""
+    def gen():
+        total = prefill + decode
+        ks, vs = [], []
+        for l in range(layers):
+            k = synth.kv_tensor((batch, heads, total, dim), seed=seed + 7 * l, key_offset=True)
+            v = synth.kv_tensor((batch, heads, total, dim), seed=seed + 7 * l + 3)
+            for t in (k, v):
+                t[:, heads // 2:, prefill:] = (t[:, heads // 2:, prefill:].float() * 2.0).to(torch.bfloat16)
+            ks.append(synth.inject_escapes(k, seed + 100 + l, left=122, right=129))
+            vs.append(synth.inject_escapes(v, seed + 200 + l, left=121, right=128))
+        yield [(ks[l][:, :, :prefill], vs[l][:, :, :prefill]) for l in range(layers)]
+        for pos in range(prefill, total):
+            yield [(ks[l][:, :, pos:pos + 1], vs[l][:, :, pos:pos + 1]) for l in range(layers)]
+    return Scenario('stress_replica', 'float11', layers,
+                    dict(right=[(129, 128)] * layers, exp_bits=[(3, 3)] * layers, **_adj()), gen)

@@ -100,3 +100,64 @@ def test_hf_generate_matches_dynamic_cache(cuda_device):
     assert torch.equal(ref, out)
     mem = cache.get_memory()
     assert mem['compressed_block_flushes'] >= 2 * 2 and mem['kv_compressed_memory'] < mem['kv_original_memory']
+
+
+def _oracle_factory():
+    """The same host classes over the CPU oracle codec (the state machine itself is pinned to the
+    reference by tests/golden/state_machine.json)."""
+    import adacode_b200.float_cache_utils as fc
+    import adacode_b200.mla_float_cache_utils as mc
+    from tests import oracle_codec
+    real = (fc.codec, mc.codec)
+
+    class Swap:
+        def __enter__(self):
+            fc.codec = mc.codec = oracle_codec
+
+        def __exit__(self, *exc):
+            fc.codec, mc.codec = real
+    return Swap()
+
+
+def test_stress_replica_gpu_equals_cpu_oracle(cuda_device):
+    """Reduced replica of the stress configuration (scale shift for half the heads, injected
+    out-of-window and zero exponents, single-token appends): the CUDA cache ends in exactly the
+    state the oracle-backed host logic ends in — every block's window, bytes and all counters."""
+    sc = scenarios.stress_scenario(batch=2, heads=4, dim=128, prefill=256, decode=300, layers=2)
+    with warnings.catch_warnings():
+        warnings.simplefilter('ignore')
+        gpu_digest, _ = scenarios.run_scenario(sc, make_cache_factory('shared'), device=cuda_device, trace_every=32)
+        with _oracle_factory():
+            cpu_digest, _ = scenarios.run_scenario(sc, make_cache_factory('shared'), device='cpu', trace_every=32)
+    assert_digest_equal(gpu_digest, cpu_digest, 'stress_replica')
+    changed = sum(l['memory']['keys_update_times'] + l['memory']['values_update_times'] for l in cpu_digest['layers'])
+    assert changed > 0, 'the schedule is meant to make the adjuster move a window'
+    assert all(l['key_segments'][0]['n_escapes'] > 0 for l in cpu_digest['layers'])
+
+
+def test_mla_true_dimensions(cuda_device):
+    """DeepSeek-V2-Lite shaped tensors: 512-dim latent, 64-dim rope key, both cache modes."""
+    import numpy as np
+    from adacode_b200 import MLAFloat11Cache
+    from oracle import float11_oracle as O
+    from tests import synth
+    cfg = scenarios.StubConfig(1, kv_lora_rank=512, qk_rope_head_dim=64)
+    lat = synth.kv_tensor((2, 1, 300, 512), seed=51, mu=-0.5, s=0.8)
+    rope = synth.kv_tensor((2, 1, 300, 64), seed=52)
+    for compress_rope in (True, False):
+        cache = MLAFloat11Cache(cfg, right=[(128, 129)], exp_bits=[(3, 4)], need_adjust=True, update_steps=128,
+                                block_size=128, compress_rope=compress_rope)
+        with warnings.catch_warnings():
+            warnings.simplefilter('error')           # dims match the config: no shape warning expected
+            cache.update(lat[:, :, :260].to(cuda_device), rope[:, :, :260].to(cuda_device), 0)
+        for t in range(260, 300):
+            a, b = cache.update(lat[:, :, t:t + 1].to(cuda_device), rope[:, :, t:t + 1].to(cuda_device), 0)
+        assert torch.equal(a.cpu().view(torch.int16), lat.view(torch.int16))
+        assert torch.equal(b.cpu().view(torch.int16), rope.view(torch.int16))
+        layer = cache.layers[0]
+        seg = layer._key_segments[0]
+        ref = O.pack_block(lat[:, :, :128].contiguous(), seg.right, seg.nbits)
+        assert np.array_equal(seg.exp_data.cpu().numpy(), ref.exp_data)
+        assert np.array_equal(seg.invalid_exp.cpu().numpy(), ref.invalid_exp)
+        mem = cache.get_memory()
+        assert mem['mla_compress_rope'] == compress_rope and mem['kv_compressed_memory'] < mem['kv_original_memory']
