@@ -36,9 +36,10 @@ if ROOT not in sys.path:
 LAYERS, KV_HEADS, PROMPT, HEAD_DIM, BLOCK = 36, 8, 20480, 128, 128
 WORKLOAD = 'config1: Qwen3-4B-shaped cache, 36 layers x K,V [1,8,20480,128] bf16, prefill packed once then unpacked'
 METRIC = 'kv_pack_unpack_bf16_equiv_GBps'
-# DRAM bytes per element of one pack launch, from the ncu capture summarised in
-# profiles/k_pack_nbits3_16x8x8192x128.md (dram read + write) / elements; None until captured.
-PACK_DRAM_BYTES_PER_ELEM = None
+# DRAM bytes per element of one pack launch (k_pack_pipe + k_compact_units, dram read + write),
+# from the ncu capture summarised in profiles/pipelined_k_pack_pipe_k_unpack_pipe_16x8x8192x128_nbits3.md;
+# scaled to a bench launch by its element count (streaming kernels: traffic is proportional to elements).
+PACK_DRAM_BYTES_PER_ELEM = 3.19
 
 
 def synth_layer(layer: int, device, seed: int, which: str):
@@ -417,13 +418,13 @@ def run_gpu_arm(args) -> None:
             'pack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (pack_ms * 1e-3) / 1e9, 1),
             'unpack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (unpack_ms * 1e-3) / 1e9, 1),
             'compression_ratio': round(ratio, 5),
-            'roofline': {'bound': 'hbm', 'kernel': 'k_pack (+ k_compact_escapes)', 'achieved': round(ach_pack, 1),
+            'roofline': {'bound': 'hbm', 'kernel': 'k_pack_pipe (+ k_compact_units)', 'achieved': round(ach_pack, 1),
                          'peak': peak, 'unit': 'GB/s', 'frac': round(ach_pack / peak, 4), 'peak_source': peak_kind,
                          'traffic': None if PACK_DRAM_BYTES_PER_ELEM is None else
                          round(PACK_DRAM_BYTES_PER_ELEM * n_elems / launches),
                          'algorithmic_bytes_per_launch': round(alg_pack / launches),
                          'avg_launch_us': round(pack_ms * 1e3 / launches, 2)},
-            'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_uniform', 'achieved': round(ach_unpack, 1),
+            'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_pipe', 'achieved': round(ach_unpack, 1),
                                 'peak': peak, 'unit': 'GB/s', 'frac': round(ach_unpack / peak, 4),
                                 'avg_launch_us': round(unpack_ms * 1e3 / launches, 2)},
             'cpu_baseline': {'value': round(2 * 2 * cpu_n / cpu_dt / 1e9, 3), 'unit': 'GB/s', 'cores': cpu_threads,
