@@ -150,6 +150,10 @@ def cpu_round_trip(blocks_per_tensor: int, tensors: int, right=130, nbits=3, see
     so that every host thread has tiles to work on).  Returns (seconds, elements, threads)."""
     import numpy as np
     from oracle import float11_oracle as O
+    try:
+        O.set_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1; use every core we may run on
+    except AttributeError:
+        O.set_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(seed)
     sigma = np.exp(rng.standard_normal((KV_HEADS, 1, HEAD_DIM))).astype(np.float32)
     data = []
