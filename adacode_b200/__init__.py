@@ -7,7 +7,10 @@ Public surface (same names as the reference package ``kv_compression``):
   ``compress_tiled_tensor``, ``materialize_tiled_state``, ``TiledCompressedTensor``   codec
   ``export_initial_compress_parameters``          best_bit_analysis_kv_cache
   ``model_config_map``                            model_configs
+and, without a reference counterpart, ``decode_attention`` (attention) — one decode step of
+attention computed from the packed planes.
 """
+from .attention import decode_attention
 from .best_bit_analysis_kv_cache import export_initial_compress_parameters
 from .codec import TiledCompressedTensor, compress_tiled_tensor, materialize_tiled_state
 from .float_cache_utils import Float11Cache, float11Layer
@@ -17,5 +20,5 @@ from .model_configs import model_config_map
 __all__ = [
     'Float11Cache', 'float11Layer', 'MLAFloat11Cache', 'MLALatentFloat11DenseRopeLayer',
     'TiledCompressedTensor', 'compress_tiled_tensor', 'materialize_tiled_state',
-    'export_initial_compress_parameters', 'model_config_map',
+    'export_initial_compress_parameters', 'model_config_map', 'decode_attention',
 ]

@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     'adacode_version', 'adacode_strerror', 'adacode_last_cuda_error', 'adacode_pack_workspace_bytes',
     'adacode_pack_tiles', 'adacode_unpack_tiles', 'adacode_unpack_segments', 'adacode_hist_bf16',
     'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host', 'adacode_pack_tiles_static',
+    'adacode_decode_attn_workspace_bytes', 'adacode_decode_attn',
 )
 
 
@@ -81,6 +82,11 @@ def lib() -> ctypes.CDLL:
     L.adacode_choose_params_host.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.adacode_calibrate_host.restype = i32
     L.adacode_calibrate_host.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    L.adacode_decode_attn_workspace_bytes.restype = sz
+    L.adacode_decode_attn_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    L.adacode_decode_attn.restype = i32
+    L.adacode_decode_attn.argtypes = [vp, i64, i64, vp, vp, i32, vp, vp, i32, i64, i64, i64,
+                                      i32, i32, i32, i32, i32, ctypes.c_float, vp, vp, sz, i32, vp, vp]
     _lib = L
     return L
 

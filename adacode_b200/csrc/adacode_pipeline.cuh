@@ -48,9 +48,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait; on expiry flags the status word and returns anyway.
+// Once any wait of the launch has timed out, the others stop waiting as well (they look at the
+// status word now and then), so that a broken launch ends in about the time of one expired wait.
+__device__ __forceinline__ bool launch_timed_out(const int32_t *status) {
+    return (*reinterpret_cast<const volatile int32_t *>(status) & ADACODE_STATUS_TIMEOUT) != 0;
+}
 __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status) {
-    for (uint32_t i = 0; i < kMaxPolls; ++i)
+    for (uint32_t i = 0; i < kMaxPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return;
+        if ((i & 4095u) == 4095u && launch_timed_out(status)) return;
+    }
     atomicOr(status, ADACODE_STATUS_TIMEOUT);
 }
 // global -> shared bulk copy, completion counted in bytes on `bar`; 16-byte aligned, size % 16 == 0
@@ -225,50 +232,24 @@ __device__ __forceinline__ TileSrc resolve_tile(const UnpackPipeArgs &a, long lo
     return t;
 }
 
-// ---- table-driven decode -------------------------------------------------------------------
-// The integer pipe (half the rate of the issue slots) is what limits these kernels, so the
-// per-element shifts, masks and adds of the decode are replaced by one shared-memory lookup per
-// pair (or quadruple, or octet) of codes: the table maps a run of packed code bits to the
-// finished exponent fields of the corresponding bf16 pairs, `(e0 << 7) | (e1 << 23)`, with the
-// window's left edge already added.  Index width: 8 bits for N = 1, 2, 4; 6 bits for N = 3.
-template <int N>
-struct DecodeLut {
-    static constexpr int index_bits = (N == 3) ? 6 : 8;
-    static constexpr int elems = index_bits / N;          // elements covered by one lookup
-    static constexpr int words = elems / 2;               // 32-bit pair words per entry
-    static constexpr int entries = 1 << index_bits;
-};
-
-__device__ __forceinline__ void build_decode_lut(uint32_t *lut, int N, int left) {
-    const int index_bits = (N == 3) ? 6 : 8;
-    const int words = (index_bits / N) / 2;
-    const int total = (1 << index_bits) * words;
-    const uint32_t mask = (1u << N) - 1u;
-    for (int w = threadIdx.x; w < total; w += kConsumerThreads) {
-        const uint32_t e = (uint32_t)(w / words), p = (uint32_t)(w % words);
-        const uint32_t c_even = (e >> (index_bits - (2 * p + 1) * N)) & mask;
-        const uint32_t c_odd = (e >> (index_bits - (2 * p + 2) * N)) & mask;
-        lut[w] = (((c_even + (uint32_t)left) & 0xFFu) << 7) | (((c_odd + (uint32_t)left) & 0xFFu) << 23);
-    }
+__device__ __forceinline__ long long shfl_ll(long long v, int src) {
+    const int lo = __shfl_sync(kFull, (int)(v & 0xFFFFFFFFll), src);
+    const int hi = __shfl_sync(kFull, (int)(v >> 32), src);
+    return ((long long)hi << 32) | (unsigned int)lo;
 }
-
-// Exponent fields of the four bf16 pairs of group word g (element 0 in the most significant bits).
-template <int N>
-__device__ __forceinline__ void decode_group(const uint32_t *lut, uint32_t g, uint32_t (&ew)[4]) {
-    if constexpr (N == 4) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) ew[i] = lut[(g >> (24 - 8 * i)) & 0xFFu];
-    } else if constexpr (N == 3) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) ew[i] = lut[(g >> (18 - 6 * i)) & 0x3Fu];
-    } else if constexpr (N == 2) {
-        const uint2 hi = reinterpret_cast<const uint2 *>(lut)[(g >> 8) & 0xFFu];
-        const uint2 lo = reinterpret_cast<const uint2 *>(lut)[g & 0xFFu];
-        ew[0] = hi.x, ew[1] = hi.y, ew[2] = lo.x, ew[3] = lo.y;
-    } else {
-        const uint4 v = reinterpret_cast<const uint4 *>(lut)[g & 0xFFu];
-        ew[0] = v.x, ew[1] = v.y, ew[2] = v.z, ew[3] = v.w;
-    }
+template <typename T>
+__device__ __forceinline__ T *shfl_ptr(T *p, int src) {
+    return reinterpret_cast<T *>(shfl_ll((long long)(uintptr_t)p, src));
+}
+// Lane `src`'s tile description, in every lane of the warp.
+__device__ __forceinline__ TileSrc shfl_tile(const TileSrc &m, int src) {
+    TileSrc t;
+    t.sm = shfl_ptr(m.sm, src), t.codes = shfl_ptr(m.codes, src), t.esc = shfl_ptr(m.esc, src);
+    t.esc_len = shfl_ll(m.esc_len, src), t.esc_start = shfl_ll(m.esc_start, src);
+    t.esc_cnt = __shfl_sync(kFull, m.esc_cnt, src);
+    t.left = __shfl_sync(kFull, m.left, src), t.nbits = __shfl_sync(kFull, m.nbits, src);
+    t.dst = shfl_ptr(m.dst, src);
+    return t;
 }
 
 template <int N>
@@ -395,58 +376,73 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
 
     if (tid >= kConsumerThreads) {
         // ---------------- producer warp ----------------
+        // Tile metadata sits behind two dependent global loads (segment record, then the tile's
+        // escape range).  Each lane resolves one of this CTA's next 32 tiles, so those round trips
+        // are paid once per 32 tiles and never between "stage free" and "loads issued".
         const int lane = tid & 31;
         uint32_t it = 0;
-        for (long long tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-            const TileSrc t = resolve_tile(a, tile);
-            // stage no more than the stream really holds, so that a short stream is reported as such
-            long long avail = t.esc_len - t.esc_start;
-            if (avail > t.esc_cnt) avail = t.esc_cnt;
-            if (avail > kEscStage) avail = kEscStage;
-            const int staged = avail > 0 ? (int)avail : 0;
-            const uint8_t *ea = t.esc + t.esc_start;
-            const int shift = (int)((uintptr_t)ea & 15);
-            for (int u = 0; u < units_per_tile; ++u, ++it) {
-                const int stg = it % kStages;
-                UnpackStage &st = s.stage[stg];
-                mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
-                // the tile's escape bytes (the same window for every unit of the tile)
+        const long long my_tiles =
+            a.n_tiles > (long long)blockIdx.x ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        for (long long base = 0; base < my_tiles; base += 32) {
+            TileSrc mine = {};
+            if (base + lane < my_tiles) mine = resolve_tile(a, blockIdx.x + (base + lane) * (long long)gridDim.x);
+            const int n_here = (int)(my_tiles - base < 32 ? my_tiles - base : 32);
+            for (int j = 0; j < n_here; ++j) {
+                const TileSrc t = shfl_tile(mine, j);
+                // stage no more than the stream really holds, so that a short stream is reported as such
+                long long avail = t.esc_len - t.esc_start;
+                if (avail > t.esc_cnt) avail = t.esc_cnt;
+                if (avail > kEscStage) avail = kEscStage;
+                int staged = avail > 0 ? (int)avail : 0;
+                const uint8_t *ea = t.esc + t.esc_start;
+                const int shift = (int)((uintptr_t)ea & 15);
+                // The window [a0, a0 + win) of whole 16-byte granules is fetched with one bulk copy.
+                // It may begin up to 15 bytes before the tile's first escape (same granule, ignored),
+                // but never reaches past the last whole granule of the stream: what lies in the
+                // stream's final partial granule is fetched with plain loads.
                 const uint8_t *a0 = ea - shift;
-                const uint8_t *lo_ok = t.esc, *hi_ok = t.esc + t.esc_len;
-                for (int wd = lane; wd * 16 < shift + staged; wd += 32) {
-                    const uint8_t *p = a0 + wd * 16;
-                    if (p >= lo_ok && p + 16 <= hi_ok) {
-                        *reinterpret_cast<uint4 *>(st.esc + wd * 16) = __ldg(reinterpret_cast<const uint4 *>(p));
-                    } else {
-                        for (int b = 0; b < 16; ++b)
-                            if (p + b >= lo_ok && p + b < hi_ok) st.esc[wd * 16 + b] = p[b];
-                    }
+                int win = (shift + staged + 15) & ~15;
+                const uintptr_t stream_end = (uintptr_t)(t.esc + t.esc_len);
+                int tail = 0;            // bytes of the final partial granule that this tile needs
+                if (staged > 0 && (uintptr_t)a0 + (uintptr_t)win > stream_end) {
+                    win -= 16;
+                    tail = (int)(stream_end & 15);
                 }
-                __syncwarp();
-                if (lane == 0) {
-                    const int row0 = u * unit_rows;
-                    const int rows = min(unit_rows, a.seq_tile - row0);
-                    const int elems = rows * a.D;
-                    const uint8_t *src_sm = t.sm + (long long)row0 * a.D;
-                    const uint8_t *src_cd = t.codes + (long long)row0 * a.D * t.nbits / 8;
-                    UnitMeta &m = st.meta;
-                    m.dst = t.dst + (long long)row0 * a.ds;
-                    m.esc = t.esc, m.esc_len = t.esc_len, m.esc_tile_start = t.esc_start;
-                    m.esc_staged = staged, m.esc_shift = shift;
-                    m.elems = elems, m.left = t.left, m.nbits = t.nbits;
-                    m.first_unit_of_tile = (u == 0);
-                    const uint32_t cbytes = (uint32_t)elems * t.nbits / 8;
-                    if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)m.dst) & 15) != 0 || (cbytes & 15) != 0 ||
-                        t.nbits < 1 || t.nbits > 4) {
-                        // never start a misaligned bulk copy: flag it and hand over an empty unit
-                        atomicOr(a.status, ADACODE_STATUS_MISALIGNED);
-                        m.elems = 0;
-                        m.nbits = 1;
-                        mbar_arrive_expect_tx(&s.full[stg], 0);
-                    } else {
-                        mbar_arrive_expect_tx(&s.full[stg], (uint32_t)elems + cbytes);
-                        bulk_load(st.sm, src_sm, (uint32_t)elems, &s.full[stg]);
-                        bulk_load(st.codes, src_cd, cbytes, &s.full[stg]);
+                if (staged == 0) win = 0;
+                for (int u = 0; u < units_per_tile; ++u, ++it) {
+                    const int stg = it % kStages;
+                    UnpackStage &st = s.stage[stg];
+                    mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
+                    if (tail > 0) {
+                        if (lane < tail) st.esc[win + lane] = a0[win + lane];
+                        __syncwarp();
+                    }
+                    if (lane == 0) {
+                        const int row0 = u * unit_rows;
+                        const int rows = min(unit_rows, a.seq_tile - row0);
+                        const int elems = rows * a.D;
+                        const uint8_t *src_sm = t.sm + (long long)row0 * a.D;
+                        const uint8_t *src_cd = t.codes + (long long)row0 * a.D * t.nbits / 8;
+                        UnitMeta &m = st.meta;
+                        m.dst = t.dst + (long long)row0 * a.ds;
+                        m.esc = t.esc, m.esc_len = t.esc_len, m.esc_tile_start = t.esc_start;
+                        m.esc_staged = staged, m.esc_shift = shift;
+                        m.elems = elems, m.left = t.left, m.nbits = t.nbits;
+                        m.first_unit_of_tile = (u == 0);
+                        const uint32_t cbytes = (uint32_t)elems * t.nbits / 8;
+                        if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)m.dst) & 15) != 0 || (cbytes & 15) != 0 ||
+                            t.nbits < 1 || t.nbits > 4) {
+                            // never start a misaligned bulk copy: flag it and hand over an empty unit
+                            atomicOr(a.status, ADACODE_STATUS_MISALIGNED);
+                            m.elems = 0;
+                            m.nbits = 1;
+                            mbar_arrive_expect_tx(&s.full[stg], 0);
+                        } else {
+                            mbar_arrive_expect_tx(&s.full[stg], (uint32_t)elems + cbytes + (uint32_t)win);
+                            bulk_load(st.sm, src_sm, (uint32_t)elems, &s.full[stg]);
+                            bulk_load(st.codes, src_cd, cbytes, &s.full[stg]);
+                            if (win > 0) bulk_load(st.esc, a0, (uint32_t)win, &s.full[stg]);
+                        }
                     }
                 }
             }
@@ -468,7 +464,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
             if (nb != lut_nbits || lf != lut_left) {
                 // uniform over the CTA: every consumer read the same meta.  The previous unit ended
                 // with a consumer barrier, so nobody still reads the old table.
-                build_decode_lut(s.lut, nb, lf);
+                build_decode_lut(s.lut, nb, lf, kConsumerThreads);
                 lut_nbits = nb, lut_left = lf;
                 consumer_sync();
             }

@@ -619,6 +619,20 @@ class float11Layer(DynamicLayer):
         self.materialize_time += time.perf_counter() - begin
         return keys, values
 
+    def decode_attention(self, query: torch.Tensor, scale: Optional[float] = None, n_splits: int = 0) -> torch.Tensor:
+        """Attention of one query token per sequence over everything this layer caches, read
+        from the packed planes and the dense residual without rebuilding dense K/V.  The
+        reference has no such path (its ``decode_impl`` is always ``'materialize_dense'``, :1342)."""
+        from . import attention
+        res_k, res_v = self._active_residual_tensors()
+        if res_k is not None and res_k.stride() != res_v.stride():
+            res_k, res_v = res_k.contiguous(), res_v.contiguous()
+        ks, vs = self._key_segments, self._value_segments
+        return attention.decode_attention(
+            query, ks, vs, res_k, res_v, scale=scale, n_splits=n_splits,
+            key_table=self._segment_table('k', ks) if ks else None,
+            value_table=self._segment_table('v', vs) if vs else None)
+
     def _empty_states(self):
         if self.cache_device is None:
             return None
@@ -744,6 +758,8 @@ class float11Layer(DynamicLayer):
         if prefill_fastpath:
             self.prefill_reuse_hits += 1
             dense_keys, dense_values = key_states, value_states
+        elif cache_kwargs is not None and cache_kwargs.get('float11_skip_materialize', False):
+            dense_keys = dense_values = None      # the caller attends to the packed planes directly
         else:
             dense_keys, dense_values = self.materialize_dense()
         return {
@@ -878,6 +894,19 @@ class Float11Cache(Cache):
         if layer_idx == len(self.layers) - 1:
             self.steps += 1
         return result['key_states'], result['value_states']
+
+    def decode_attention(self, query: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                         layer_idx: int, scale: Optional[float] = None, n_splits: int = 0) -> torch.Tensor:
+        """One decode step of one layer without dense K/V: append the new token's ``key_states``
+        / ``value_states`` ([B, Hkv, 1, D]) exactly as ``update`` does (same packing schedule and
+        adjuster steps), then return ``softmax(scale * q K^T) V`` for ``query`` ([B, Hq, 1, D] or
+        [B, Hq, D]) over the whole cache, computed from the packed planes.  Results are fp32
+        attention rounded to bf16; they are close to, not bit-identical with, what a model's own
+        attention kernel gives on the dense K/V that ``update`` returns."""
+        if key_states.shape[-2] != 1:
+            raise ValueError('decode_attention appends exactly one token per sequence; use update() for prefill')
+        self.update(key_states, value_states, layer_idx, {'float11_skip_materialize': True})
+        return self.layers[layer_idx].decode_attention(query, scale=scale, n_splits=n_splits)
 
     def get_layer_cache_view(self, layer_idx: int):
         return self.layers[layer_idx].get_cache_view()

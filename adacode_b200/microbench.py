@@ -48,6 +48,54 @@ def _time(fn, iters: int, warmup: int) -> float:
     return times[len(times) // 2] * 1e-3
 
 
+def attention_main(args) -> None:
+    """One decode step over a cache of shape --shape for K and for V: the fused kernel reads
+    (1 + nbits/8 + p) bytes per cached element; the materialising path reads them too, writes
+    2 bytes and lets the attention kernel read 2 bytes again."""
+    import torch.nn.functional as F
+
+    from . import attention
+    shape = tuple(int(v) for v in args.shape.split(','))
+    B, H, S, D = shape
+    Hq = args.attention
+    dev = torch.device('cuda', 0)
+    k = synthetic_keys(shape, seed=0, device=dev)
+    v = synthetic_keys(shape, seed=1, device=dev)
+    kc, _ = codec.pack_blocks(k, args.right, args.nbits, 128)
+    vc, _ = codec.pack_blocks(v, args.right, args.nbits, 128)
+    ks, vs = kc.segments(), vc.segments()
+    kt = codec.build_segment_table(ks, None, dev)
+    vt = codec.build_segment_table(vs, None, dev)
+    q = (torch.randn(B, Hq, D, device=dev) * 0.3).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    p = (kc.n_escapes + vc.n_escapes) / (2 * k.numel())
+
+    def fused():
+        attention.decode_attention(q, ks, vs, key_table=kt, value_table=vt, out=out)
+
+    def materialise():
+        codec.unpack_segments(ks, dk, table=kt)
+        codec.unpack_segments(vs, dv, table=vt)
+        return F.scaled_dot_product_attention(q.unsqueeze(2), dk, dv, enable_gqa=Hq != H)
+
+    def dense_only():
+        return F.scaled_dot_product_attention(q.unsqueeze(2), dk, dv, enable_gqa=Hq != H)
+
+    t_f = _time(fused, args.iters, args.warmup)
+    t_m = _time(materialise, args.iters, args.warmup)
+    t_d = _time(dense_only, args.iters, args.warmup)
+    ref = materialise()[:, :, 0].float()
+    err = (out.float() - ref).abs().max().item()
+    packed_bytes = 2 * k.numel() * (1.0 + args.nbits / 8.0 + p)
+    for name, t in (('decode_attn_fused', t_f), ('unpack_then_sdpa', t_m), ('sdpa_on_dense_only', t_d)):
+        print(json.dumps({
+            'kernel': name, 'shape': list(shape), 'q_heads': Hq, 'nbits': args.nbits, 'escape_fraction': round(p, 5),
+            'us': round(t * 1e6, 1), 'packed_GBps': round(packed_bytes / t / 1e9, 1),
+            'bf16_equiv_GBps': round(4 * k.numel() / t / 1e9, 1), 'max_abs_diff_vs_sdpa': round(err, 5),
+        }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument('--shape', default='16,8,8192,128')
@@ -57,7 +105,12 @@ def main() -> None:
     ap.add_argument('--iters', type=int, default=5)
     ap.add_argument('--warmup', type=int, default=2)
     ap.add_argument('--no-hist', action='store_true')
+    ap.add_argument('--attention', type=int, default=0, metavar='HQ',
+                    help='time decode attention with HQ query heads instead: fused (packed planes) '
+                         'against unpack + torch SDPA over dense K/V')
     args = ap.parse_args()
+    if args.attention:
+        return attention_main(args)
     shape = tuple(int(v) for v in args.shape.split(','))
     B, H, S, D = shape
     dev = torch.device('cuda', 0)

@@ -196,6 +196,37 @@ int adacode_choose_params_host(const int64_t *hist256, int *right, int *nbits);
  */
 int adacode_calibrate_host(const int64_t *hist256, int *right, int *nbits);
 
+/*
+ * Bytes of scratch adacode_decode_attn needs (split partials, fp32).  n_splits <= 0 sizes for
+ * the largest split count the library will pick itself.
+ */
+size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);
+
+/*
+ * Single-query ("decode step") attention computed straight from the packed cache:
+ *   out[b][hq] = softmax(scale * q[b][hq] . K[b][hq / G]^T) V[b][hq / G],  G = Hq / Hkv,
+ * where K and V are n_segments packed 128-token segments each (device arrays of segment
+ * records in sequence order; dst_seq_offset is ignored) followed by tail_len dense bf16
+ * tokens (the cache's not-yet-packed residual, element strides tail_stride_b/h/s, unit
+ * stride along D).  Every cached token is visible to the query (no mask).  The planes are
+ * decoded tile by tile in shared memory, so HBM sees the packed bytes only; the work is
+ * split along the sequence into n_splits parts (<= 0: chosen by the library, at most 64)
+ * whose partial results a second kernel merges.
+ * The reference implementation has no counterpart: its caches report
+ *   decode_impl 'materialize_dense' (float_cache_utils.py:1342) and always rebuild dense K/V
+ *   (float11Layer.update, :1278-1316) before the model's own attention runs; the module its
+ *   validation script imports for a fused path (ops/kv_attention.py) is not in its tree.
+ * Arithmetic: products and sums in fp32, probabilities kept in fp32, output rounded to bf16
+ * (nearest even).  Requirements: seq_tile == 128, D in {64, 128}, G <= 8, q with unit stride
+ * along D and element strides q_stride_b/h, out contiguous [B][Hq][D].
+ */
+int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride_h,
+                        const adacode_segment *k_segments_dev, const adacode_segment *v_segments_dev, int n_segments,
+                        const void *k_tail_bf16, const void *v_tail_bf16, int tail_len, int64_t tail_stride_b,
+                        int64_t tail_stride_h, int64_t tail_stride_s, int B, int Hq, int Hkv, int seq_tile, int D,
+                        float scale, void *out_bf16, void *workspace, size_t workspace_bytes, int n_splits,
+                        int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

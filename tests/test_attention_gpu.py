@@ -1,0 +1,155 @@
+"""Fused unpack + decode attention (``adacode_decode_attn``) against an fp32 PyTorch attention
+over the same (losslessly cached) K and V.
+
+This is floating-point work, so the bar is a tolerance, not bit equality.  The kernel keeps
+products, sums and probabilities in fp32 and rounds the result to bf16 once, so the expected
+error is one bf16 rounding (relative 2**-9) plus fp32 summation-order and fast-exp noise:
+``|out - ref| <= 2**-8 * |ref| + 2e-3 * max|ref|`` is asserted for every output element.
+"""
+import math
+
+import pytest
+import torch
+
+from tests import synth
+from tests.scenarios import StubConfig
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 2.0 ** -8
+ATOL_FRAC = 2e-3
+
+
+def _reference(q, k, v, scale):
+    """fp32 attention of q [B, Hq, D] over k, v [B, Hkv, S, D] with grouped heads."""
+    B, Hq, D = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    kf = k.float().repeat_interleave(G, dim=1)
+    vf = v.float().repeat_interleave(G, dim=1)
+    scores = torch.einsum('bhd,bhsd->bhs', q.float(), kf) * scale
+    return torch.einsum('bhs,bhsd->bhd', torch.softmax(scores, dim=-1), vf)
+
+
+def _assert_close(out, ref):
+    out = out.float()
+    bound = RTOL * ref.abs() + ATOL_FRAC * ref.abs().max()
+    err = (out - ref).abs()
+    worst = (err - bound).max().item()
+    assert worst <= 0, f'max excess error {worst:.3e} (max err {err.max().item():.3e}, max ref {ref.abs().max().item():.3e})'
+
+
+def _pack_mixed(x, params):
+    """Pack x [B, H, S, D] block by block, block j with params[j % len(params)] = (right, nbits)."""
+    from adacode_b200 import codec
+    segs = []
+    for j in range(x.shape[2] // 128):
+        right, nbits = params[j % len(params)]
+        chunk, _ = codec.pack_blocks(x[:, :, j * 128:(j + 1) * 128], right, nbits, 128)
+        segs.append(chunk.segment(0))
+    return segs
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,D,n_seg,tail', [
+    (1, 8, 8, 128, 3, 0),        # multi-head attention, packed only
+    (2, 32, 8, 128, 5, 77),      # grouped queries, ragged dense tail
+    (1, 16, 2, 128, 2, 128),     # eight query heads per KV head, full dense block staged
+    (3, 4, 4, 64, 4, 1),         # head_dim 64, one dense token
+    (1, 8, 2, 64, 0, 200),       # nothing packed yet
+    (2, 8, 1, 128, 9, 300),      # multi-query attention, tail longer than two tiles
+])
+@pytest.mark.parametrize('n_splits', [0, 1, 7])
+def test_matches_fp32_attention(cuda_device, B, Hq, Hkv, D, n_seg, tail, n_splits):
+    from adacode_b200 import attention, codec
+    S = n_seg * 128 + tail
+    k_cpu = synth.kv_tensor((B, Hkv, S, D), seed=11, key_offset=True, s=0.5)
+    v_cpu = synth.kv_tensor((B, Hkv, S, D), seed=12, s=0.5)
+    k, v = k_cpu.to(cuda_device), v_cpu.to(cuda_device)
+    g = torch.Generator('cpu').manual_seed(5)
+    q = (torch.randn(B, Hq, D, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+    scale = 1.0 / math.sqrt(D)
+    kseg = _pack_mixed(k[:, :, :n_seg * 128], [(130, 3), (129, 4), (128, 2)])
+    vseg = _pack_mixed(v[:, :, :n_seg * 128], [(127, 3), (126, 1), (128, 4)])
+    # dense tails live in a larger buffer, as the cache's residual does (non-trivial strides)
+    k_tail = v_tail = None
+    if tail:
+        kbuf = torch.zeros(B, Hkv, tail + 50, D, dtype=torch.bfloat16, device=cuda_device)
+        vbuf = torch.zeros_like(kbuf)
+        kbuf[:, :, :tail] = k[:, :, n_seg * 128:]
+        vbuf[:, :, :tail] = v[:, :, n_seg * 128:]
+        k_tail, v_tail = kbuf[:, :, :tail], vbuf[:, :, :tail]
+    out = attention.decode_attention(q, kseg, vseg, k_tail, v_tail, scale=scale, n_splits=n_splits)
+    codec.check_device_status(cuda_device)
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    _assert_close(out, _reference(q, k, v, scale))
+
+
+def test_escape_heavy_planes_and_peaked_softmax(cuda_device):
+    """Windows that miss most exponents (every second element escapes) and scores large enough
+    that a handful of tokens carry all the probability mass."""
+    from adacode_b200 import attention, codec
+    B, Hq, Hkv, D, n_seg = 2, 8, 2, 128, 6
+    k_cpu = synth.inject_escapes(synth.kv_tensor((B, Hkv, n_seg * 128, D), seed=3, key_offset=True), 9, 118, 125, p_window=0.01)
+    v_cpu = synth.kv_tensor((B, Hkv, n_seg * 128, D), seed=4)
+    k, v = k_cpu.to(cuda_device), v_cpu.to(cuda_device)
+    # inject_escapes can create huge magnitudes; keep keys finite and moderate for a meaningful softmax
+    k = torch.nan_to_num(k.float(), nan=0.0, posinf=0.0, neginf=0.0).clamp(-64, 64).to(torch.bfloat16)
+    g = torch.Generator('cpu').manual_seed(6)
+    q = (torch.randn(B, Hq, D, generator=g) * 2.0).to(torch.bfloat16).to(cuda_device)
+    kseg = _pack_mixed(k, [(125, 2), (121, 1)])
+    vseg = _pack_mixed(v, [(124, 1), (127, 2)])
+    assert sum(s.invalid_exp.numel() for s in kseg) > 0.2 * k.numel()
+    out = attention.decode_attention(q, kseg, vseg, scale=0.25)
+    codec.check_device_status(cuda_device)
+    _assert_close(out, _reference(q, k, v, 0.25))
+
+
+def test_cache_decode_attention_follows_update_schedule(cuda_device):
+    """``Float11Cache.decode_attention`` must leave the cache in the state ``update`` leaves it in
+    (same packed segments, same adjuster decisions) and agree with attention over the dense K/V
+    that a twin cache returns from ``update``, step by step across block boundaries."""
+    from adacode_b200 import Float11Cache
+    B, Hq, Hkv, D, L = 2, 8, 2, 128, 2
+    cfg = StubConfig(L)
+    kw = dict(need_adjust=True, update_steps=128, block_size=128, layout='segmented_tiled')
+    fused = Float11Cache(cfg, 129, 3, **kw)
+    dense = Float11Cache(cfg, 129, 3, dense_workspace='layer', **kw)
+    prefill = 300
+    steps = 140
+    k_all = synth.kv_tensor((B, Hkv, prefill + steps, D), seed=21, key_offset=True, s=0.5).to(cuda_device)
+    v_all = synth.kv_tensor((B, Hkv, prefill + steps, D), seed=22, s=0.5).to(cuda_device)
+    g = torch.Generator('cpu').manual_seed(23)
+    qs = (torch.randn(steps, B, Hq, 1, D, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+    for layer in range(L):
+        fused.update(k_all[:, :, :prefill], v_all[:, :, :prefill], layer)
+        dense.update(k_all[:, :, :prefill], v_all[:, :, :prefill], layer)
+    scale = 1.0 / math.sqrt(D)
+    for t in range(steps):
+        pos = prefill + t
+        for layer in range(L):
+            kt, vt = k_all[:, :, pos:pos + 1], v_all[:, :, pos:pos + 1]
+            out = fused.decode_attention(qs[t], kt, vt, layer)
+            kd, vd = dense.update(kt, vt, layer)
+            assert kd.shape[2] == pos + 1
+            _assert_close(out[:, :, 0], _reference(qs[t][:, :, 0], kd, vd, scale))
+    for lf, ld in zip(fused.layers, dense.layers):
+        assert lf.segment_params() == ld.segment_params()
+        assert lf.get_seq_length() == ld.get_seq_length() == prefill + steps
+    mf, md = fused.get_memory(), dense.get_memory()
+    for key in ('kv_compressed_memory', 'kv_original_memory', 'compressed_block_flushes', 'keys_update_times'):
+        assert mf[key] == md[key]
+    assert mf['materialize_calls'] == 0
+
+
+def test_rejects_unsupported_shapes(cuda_device):
+    from adacode_b200 import attention
+    k = synth.kv_tensor((1, 1, 128, 128), seed=1).to(cuda_device)
+    q16 = torch.zeros(1, 16, 128, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError):
+        attention.decode_attention(q16, [], [], k, k)              # sixteen query heads per KV head
+    k96 = synth.kv_tensor((1, 1, 128, 96), seed=1).to(cuda_device)
+    q96 = torch.zeros(1, 1, 96, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError):
+        attention.decode_attention(q96, [], [], k96, k96)          # head_dim outside {64, 128}
+    with pytest.raises(ValueError):
+        attention.decode_attention(q16[:, :1], [], [])             # empty cache
