@@ -205,7 +205,7 @@ __device__ __forceinline__ int warp_scan4(const int cnt[kCPT], int incl[kCPT]) {
 // per-element shifts, masks and adds of the decode are replaced by one shared-memory lookup per
 // pair (or quadruple, or octet) of codes: the table maps a run of packed code bits to the
 // finished exponent fields of the corresponding bf16 pairs, `(e0 << 7) | (e1 << 23)`, with the
-// window's left edge already added.  Index width: 8 bits for N = 1, 2, 4; 6 bits for N = 3.
+// window's left edge already added (and 0 for code 0).  Index width: 8 bits for N = 1, 2, 4; 6 bits for N = 3.
 template <int N>
 struct DecodeLut {
     static constexpr int index_bits = (N == 3) ? 6 : 8;
@@ -223,7 +223,10 @@ __device__ __forceinline__ void build_decode_lut(uint32_t *lut, int N, int left,
         const uint32_t e = (uint32_t)(w / words), p = (uint32_t)(w % words);
         const uint32_t c_even = (e >> (index_bits - (2 * p + 1) * N)) & mask;
         const uint32_t c_odd = (e >> (index_bits - (2 * p + 2) * N)) & mask;
-        lut[w] = (((c_even + (uint32_t)left) & 0xFFu) << 7) | (((c_odd + (uint32_t)left) & 0xFFu) << 23);
+        // code 0 (an escape) decodes to exponent field 0, so that the escaped exponent can be OR-ed in
+        const uint32_t e_even = c_even ? ((c_even + (uint32_t)left) & 0xFFu) : 0u;
+        const uint32_t e_odd = c_odd ? ((c_odd + (uint32_t)left) & 0xFFu) : 0u;
+        lut[w] = (e_even << 7) | (e_odd << 23);
     }
 }
 

@@ -308,15 +308,19 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
             if (zc[k] != 0) {
                 int r = consumed + wprefix + incl[k] - zc[k];     // rank inside the tile
                 if (r + zc[k] <= m.esc_staged) {
+                    // the exponent field in s.out is zero at escaped positions (code 0 decodes to 0),
+                    // so the escape byte is OR-ed in with a shared-memory reduction: no
+                    // read-modify-write round trip in this thread
                     const uint8_t *ep = st.esc + m.esc_shift + r;
+                    uint32_t *ow32 = reinterpret_cast<uint32_t *>(ow);
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         uint32_t z = zm[k][q];
                         while (z) {
                             const int pos = 31 - __clz(z);
                             z ^= 1u << pos;
-                            uint16_t *pw = ow + (q * 8 + 7 - pos / N);
-                            *pw = (uint16_t)((*pw & 0x807Fu) | ((uint32_t)(*ep++) << 7));
+                            const int el = q * 8 + 7 - pos / N;
+                            atomicOr(ow32 + (el >> 1), (uint32_t)(*ep++) << (7 + 16 * (el & 1)));
                         }
                     }
                 } else {
