@@ -15,9 +15,13 @@
 
 #include "adacode.h"
 
+#include <stdlib.h>
+
 namespace {
 
 #include "adacode_device.cuh"
+#define ADACODE_PIPELINE_UNPACK_ONLY
+#include "adacode_pipeline.cuh"
 
 constexpr int kAttnThreads = 128;
 constexpr int kTileTokens = 128;
@@ -167,7 +171,7 @@ __device__ __forceinline__ void load_dense_tile(AttnSmem &s, const uint16_t *bas
 }
 
 __global__ void __launch_bounds__(kAttnThreads) k_decode_attn(const AttnArgs a) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     AttnSmem &s = *reinterpret_cast<AttnSmem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, bh = blockIdx.y;
@@ -309,11 +313,409 @@ __global__ void k_decode_attn_combine(const float *__restrict__ part_o, const fl
     out[(long long)bhq * D + d] = (uint16_t)(u >> 16);
 }
 
-int pick_splits(int B, int Hkv, int items) {
+// =======================================================================================
+// Pipelined variant for head_dim 128: the unpack pipeline (producer warp, bulk copies into a
+// two-stage ring, 16 consumer warps decoding out of shared memory) feeding tensor-core products.
+// A decoded tile lives in shared memory as 128 rows (tokens) of 256 bytes whose 16-byte pieces are
+// XOR-swizzled with the row index, so that ldmatrix reads it without bank conflicts both as
+// K (token-major, for scores) and, transposed, as V (for the weighted sum).
+//   scores  S[t][g]   = sum_d K[t][d] q[g][d]   : mma.m16n8k16, A = K rows, B = q (8 query heads)
+//   output  O^T[d][g] = sum_t V[t][d] P[t][g]   : mma.m16n8k16, A = V^T (ldmatrix.trans), B = P
+// Warps 0..7 own 16 tokens (scores) resp. 16 output columns (weighted sum) each.
+// =======================================================================================
+
+constexpr int kAD = 128;                 // head_dim of this variant
+constexpr int kQPad = kAD + 8;           // padded rows of the small operand matrices (272 bytes)
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnPipeSmem {
+    UnpackStage stage[kStages];
+    alignas(128) uint8_t tile[kTileTokens * kAD * 2];
+    alignas(16) uint32_t lut[2][1024];            // [0] keys, [1] values
+    alignas(16) uint16_t q[kMaxGroup][kQPad];     // queries, bf16
+    alignas(16) uint16_t p[kMaxGroup][kQPad];     // probabilities of the current tile, bf16, [head][token]
+    float red_max[8][kMaxGroup];                  // per-warp partial maxima
+    float red_sum[8][kMaxGroup];                  // per-warp partial sums
+    float m[2][kMaxGroup];                        // running max (log2 domain), double-buffered by tile parity
+    float l[kMaxGroup];
+    float alpha[kMaxGroup];
+    alignas(8) uint64_t full[kStages];
+    alignas(8) uint64_t empty[kStages];
+    int warp_tot[kPWarps];
+};
+
+__device__ __forceinline__ uint32_t swz(int row, int piece) {
+    return (uint32_t)(row * 256 + ((piece ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
+    uint32_t u = __float_as_uint(x);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return u >> 16;
+}
+
+// Decode one staged unit (a whole 128 x 128 tile) into the swizzled tile.  Same steps as the
+// unpack kernel's consumer: zero-slot masks, warp scan, cross-warp prefix (one barrier), table
+// decode, escapes OR-ed in.  Ends with a consumer barrier: the tile is complete on return.
+template <int N>
+__device__ __forceinline__ void decode_unit_swz(AttnPipeSmem &s, const UnpackStage &st, uint64_t *empty_bar,
+                                                const uint32_t *lut, int32_t *status) {
+    constexpr int CB = 2 * N;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const UnitMeta m = st.meta;
+    const int chunks = m.elems >> 4;
+
+    uint4 o[kPCPT][2];
+    uint32_t zm[kPCPT][2];
+    int zc[kPCPT];
+#pragma unroll
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        uint32_t g[2] = {0u, 0u};
+        uint4 sv = make_uint4(0, 0, 0, 0);
+        const bool valid = c < chunks;
+        if (valid) {
+            sv = *reinterpret_cast<const uint4 *>(st.sm + c * 16);
+            load_chunk_codes<N, 16>(st.codes + c * CB, g);
+        }
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        zc[k] = 0;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            zm[k][q] = valid ? zero_slots<N>(g[q]) : 0u;
+            zc[k] += __popc(zm[k][q]);
+            uint32_t ew[4];
+            decode_group<N>(lut, g[q], ew);
+            const uint32_t s0 = sw[2 * q], s1 = sw[2 * q + 1];
+            o[k][q].x = ew[0] | (__byte_perm(s0, 0u, 0x1100) & 0x807F807Fu);
+            o[k][q].y = ew[1] | (__byte_perm(s0, 0u, 0x3322) & 0x807F807Fu);
+            o[k][q].z = ew[2] | (__byte_perm(s1, 0u, 0x1100) & 0x807F807Fu);
+            o[k][q].w = ew[3] | (__byte_perm(s1, 0u, 0x3322) & 0x807F807Fu);
+        }
+    }
+    int incl[kPCPT];
+    const int wtot = warp_scan_counts(zc, incl);
+    if (lane == 0) s.warp_tot[warp] = wtot;
+    consumer_sync();           // also: every warp is done reading the previous tile
+    int wprefix, unit_tot;
+    cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+#pragma unroll
+    for (int k = 0; k < kPCPT; ++k) {
+        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        if (c < chunks) {
+            const int row = c >> 3, piece = (c & 7) * 2;
+            uint8_t *p0 = s.tile + swz(row, piece), *p1 = s.tile + swz(row, piece + 1);
+            *reinterpret_cast<uint4 *>(p0) = o[k][0];
+            *reinterpret_cast<uint4 *>(p1) = o[k][1];
+            if (zc[k] != 0) {
+                int r = wprefix + incl[k] - zc[k];     // rank inside the tile
+                if (r + zc[k] <= m.esc_staged) {
+                    const uint8_t *ep = st.esc + m.esc_shift + r;
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        uint32_t z = zm[k][q];
+                        uint32_t *w32 = reinterpret_cast<uint32_t *>(q == 0 ? p0 : p1);
+                        while (z) {
+                            const int pos = 31 - __clz(z);
+                            z ^= 1u << pos;
+                            const int el = 7 - pos / N;
+                            atomicOr(w32 + (el >> 1), (uint32_t)(*ep++) << (7 + 16 * (el & 1)));
+                        }
+                    }
+                } else {
+                    // beyond the staged window (or beyond the stream): fetch from global memory
+#pragma unroll 1
+                    for (int q = 0; q < 2; ++q) {
+                        uint32_t z = zm[k][q];
+                        uint32_t *w32 = reinterpret_cast<uint32_t *>(q == 0 ? p0 : p1);
+                        while (z) {
+                            const int pos = 31 - __clz(z);
+                            z ^= 1u << pos;
+                            const int el = 7 - pos / N;
+                            uint32_t e = 0;
+                            if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
+                            else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
+                            else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
+                            ++r;
+                            atomicOr(w32 + (el >> 1), e << (7 + 16 * (el & 1)));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    mbar_arrive(empty_bar);
+    consumer_sync();
+}
+
+// Dense rows [t0, t0 + 128) of `base` into the swizzled tile, zero beyond `len`.  Barrier before
+// (the previous tile is no longer read) and after (the tile is complete).
+__device__ __forceinline__ void load_dense_tile_swz(AttnPipeSmem &s, const uint16_t *base, long long ss, int t0, int len) {
+    consumer_sync();
+    for (int i = threadIdx.x; i < kTileTokens * (kAD / 2); i += kConsumerThreads) {
+        const int row = i >> 6, w = i & 63;
+        uint32_t v = 0;
+        if (t0 + row < len) v = *reinterpret_cast<const uint32_t *>(base + (long long)(t0 + row) * ss + 2 * w);
+        *reinterpret_cast<uint32_t *>(s.tile + swz(row, w >> 2) + (w & 3) * 4) = v;
+    }
+    consumer_sync();
+}
+
+struct AttnPipeArgs {
+    AttnArgs a;
+    UnpackPipeArgs k, v;      // table form, used through resolve_tile
+};
+
+// Scores of the K tile in shared memory against the group's queries, online-softmax bookkeeping
+// and the tile's probabilities (bf16, s.p).  Called by all consumer warps; warps 0..7 work (and meet
+// at a barrier of their own), the others go straight on to the next unit's register phase.
+__device__ __forceinline__ void score_tile(AttnPipeSmem &s, int valid, float sc2, int parity) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g0 = 2 * (lane & 3), r0 = lane >> 2;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    if (warp < 8) {
+        const uint32_t tile_base = smem_u32(s.tile);
+        const int t0 = warp * 16;
+        const int lrow = t0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int lp = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < kAD / 16; ++ks) {
+            uint32_t af[4];
+            ldsm_x4(tile_base + swz(lrow, 2 * ks + lp), af);
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&s.q[r0][16 * ks + g0]);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&s.q[r0][16 * ks + 8 + g0]);
+            mma_bf16(c, af, b0, b1);
+        }
+        const int ta = t0 + r0, tb = ta + 8;
+        c[0] = ta < valid ? c[0] * sc2 : -INFINITY;
+        c[1] = ta < valid ? c[1] * sc2 : -INFINITY;
+        c[2] = tb < valid ? c[2] * sc2 : -INFINITY;
+        c[3] = tb < valid ? c[3] * sc2 : -INFINITY;
+        float v0 = fmaxf(c[0], c[2]), v1 = fmaxf(c[1], c[3]);
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+            v0 = fmaxf(v0, __shfl_xor_sync(kFull, v0, d));
+            v1 = fmaxf(v1, __shfl_xor_sync(kFull, v1, d));
+        }
+        if (lane < 4) {
+            s.red_max[warp][g0] = v0;
+            s.red_max[warp][g0 + 1] = v1;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");      // the eight math warps only; the others run ahead
+        float mn[2], al[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float tm = s.red_max[0][g0 + j];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) tm = fmaxf(tm, s.red_max[w][g0 + j]);
+            const float mo = s.m[parity][g0 + j];
+            mn[j] = fmaxf(mo, tm);
+            al[j] = mo == -INFINITY ? 0.f : exp2f(mo - mn[j]);
+        }
+        // probabilities, rounded to bf16 (what the tensor cores multiply with; the sums use the same)
+        const uint32_t b00 = f32_to_bf16_bits(c[0] == -INFINITY ? 0.f : exp2f(c[0] - mn[0]));
+        const uint32_t b01 = f32_to_bf16_bits(c[1] == -INFINITY ? 0.f : exp2f(c[1] - mn[1]));
+        const uint32_t b10 = f32_to_bf16_bits(c[2] == -INFINITY ? 0.f : exp2f(c[2] - mn[0]));
+        const uint32_t b11 = f32_to_bf16_bits(c[3] == -INFINITY ? 0.f : exp2f(c[3] - mn[1]));
+        s.p[g0][ta] = (uint16_t)b00;
+        s.p[g0 + 1][ta] = (uint16_t)b01;
+        s.p[g0][ta + 8] = (uint16_t)b10;
+        s.p[g0 + 1][ta + 8] = (uint16_t)b11;
+        float s0 = __uint_as_float(b00 << 16) + __uint_as_float(b10 << 16);
+        float s1 = __uint_as_float(b01 << 16) + __uint_as_float(b11 << 16);
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+            s0 += __shfl_xor_sync(kFull, s0, d);
+            s1 += __shfl_xor_sync(kFull, s1, d);
+        }
+        if (lane < 4) {
+            s.red_sum[warp][g0] = s0;
+            s.red_sum[warp][g0 + 1] = s1;
+            if (warp == 0) {
+                s.m[parity ^ 1][g0] = mn[0];
+                s.m[parity ^ 1][g0 + 1] = mn[1];
+                s.alpha[g0] = al[0];
+                s.alpha[g0 + 1] = al[1];
+            }
+        }
+    }
+}
+
+// oacc = oacc * alpha + V^T P for the V tile in shared memory; warp 0 also folds the tile's
+// probability sums into the running denominators.  The caller has passed a barrier since score_tile.
+__device__ __forceinline__ void accumulate_tile(AttnPipeSmem &s, float (&oacc)[4]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g0 = 2 * (lane & 3), r0 = lane >> 2;
+    if (warp >= 8) return;
+    const float a0 = s.alpha[g0], a1 = s.alpha[g0 + 1];
+    oacc[0] *= a0, oacc[1] *= a1, oacc[2] *= a0, oacc[3] *= a1;
+    const uint32_t tile_base = smem_u32(s.tile);
+    const int m_piece = warp * 2 + ((lane >> 3) & 1);            // output columns 16 warp .. 16 warp + 15
+    const int lt = (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+    for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+        uint32_t af[4];
+        ldsm_x4_trans(tile_base + swz(16 * ks + lt, m_piece), af);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&s.p[r0][16 * ks + g0]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&s.p[r0][16 * ks + 8 + g0]);
+        mma_bf16(oacc, af, b0, b1);
+    }
+    if (warp == 0 && lane < kMaxGroup) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += s.red_sum[w][lane];
+        s.l[lane] = s.l[lane] * s.alpha[lane] + t;
+    }
+}
+
+__global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const AttnPipeArgs pa) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    AttnPipeSmem &s = *reinterpret_cast<AttnPipeSmem *>(smem_raw);
+    const AttnArgs &a = pa.a;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int split = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / a.Hkv, hkv = bh - b * a.Hkv;
+    const int G = a.G;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], kConsumerThreads);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // queries (zero rows beyond G), running statistics
+    for (int i = tid; i < kMaxGroup * kQPad; i += kPipeThreads) {
+        const int g = i / kQPad, d = i - g * kQPad;
+        uint16_t v = 0;
+        if (g < G && d < kAD) v = a.q[(long long)b * a.q_sb + (long long)(hkv * G + g) * a.q_sh + d];
+        s.q[g][d] = v;
+        s.p[g][d] = 0;
+    }
+    if (tid < kMaxGroup) {
+        s.m[0][tid] = s.m[1][tid] = -INFINITY;
+        s.l[tid] = 0.f;
+        s.alpha[tid] = 0.f;
+    }
+    __syncthreads();
+
+    const int tail_tiles = (a.tail_len + kTileTokens - 1) / kTileTokens;
+    const int items = a.n_seg + tail_tiles;
+    const int first = (int)((long long)items * split / a.n_splits);
+    const int last = (int)((long long)items * (split + 1) / a.n_splits);
+    const int pk_first = first < a.n_seg ? first : a.n_seg;
+    const int pk_last = last < a.n_seg ? last : a.n_seg;
+    const int n_units = 2 * (pk_last - pk_first);          // K tile, V tile, K tile, ...
+
+    if (tid >= kConsumerThreads) {
+        // ---------------- producer warp ----------------
+        uint32_t it = 0;
+        for (int base = 0; base < n_units; base += 32) {
+            TileSrc mine = {};
+            const int u = base + lane;
+            if (u < n_units) {
+                const long long tile = (long long)(pk_first + (u >> 1)) * pa.k.BH + bh;
+                mine = (u & 1) ? resolve_tile(pa.v, tile) : resolve_tile(pa.k, tile);
+            }
+            const int n_here = n_units - base < 32 ? n_units - base : 32;
+            for (int j = 0; j < n_here; ++j, ++it) {
+                const TileSrc t = shfl_tile(mine, j);
+                const EscWindow w = esc_window(t);
+                const int stg = it % kStages;
+                mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
+                issue_unit(s.stage[stg], &s.full[stg], t, w, 0, kTileTokens, kAD, nullptr, true, a.status);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    const float sc2 = a.scale * kLog2e;                      // scores are kept in the log2 domain
+    float oacc[4] = {0.f, 0.f, 0.f, 0.f};                    // O^T[d = 16 warp + lane/4 (+8)][2 (lane%4), +1]
+    int parity = 0;                                          // tiles seen & 1: which m[] holds the running max
+    int lut_left[2] = {0, 0}, lut_nbits[2] = {0, 0};
+    for (int u = 0; u < n_units; ++u) {
+        const int stg = u % kStages, which = u & 1;
+        if (lane == 0) mbar_wait(&s.full[stg], (u / kStages) & 1, a.status);
+        __syncwarp();
+        const UnpackStage &st = s.stage[stg];
+        const int nb = st.meta.nbits, lf = st.meta.left;
+        if (nb != lut_nbits[which] || lf != lut_left[which]) {
+            // uniform over the CTA; the previous user of this table finished before the last barrier
+            build_decode_lut(s.lut[which], nb, lf, kConsumerThreads);
+            lut_nbits[which] = nb, lut_left[which] = lf;
+            consumer_sync();
+        }
+        switch (nb) {
+            case 1: decode_unit_swz<1>(s, st, &s.empty[stg], s.lut[which], a.status); break;
+            case 2: decode_unit_swz<2>(s, st, &s.empty[stg], s.lut[which], a.status); break;
+            case 3: decode_unit_swz<3>(s, st, &s.empty[stg], s.lut[which], a.status); break;
+            default: decode_unit_swz<4>(s, st, &s.empty[stg], s.lut[which], a.status); break;
+        }
+        if (which == 0) {
+            score_tile(s, kTileTokens, sc2, parity);
+        } else {
+            accumulate_tile(s, oacc);
+            parity ^= 1;
+        }
+    }
+    // dense residual tiles that fall into this split
+    const int tl_first = first > a.n_seg ? first - a.n_seg : 0;
+    const int tl_last = last > a.n_seg ? last - a.n_seg : 0;
+    for (int j = tl_first; j < tl_last; ++j) {
+        const int t0 = j * kTileTokens;
+        const int valid = a.tail_len - t0 < kTileTokens ? a.tail_len - t0 : kTileTokens;
+        const long long off = (long long)b * a.t_sb + (long long)hkv * a.t_sh;
+        load_dense_tile_swz(s, a.k_tail + off, a.t_ss, t0, a.tail_len);
+        score_tile(s, valid, sc2, parity);
+        load_dense_tile_swz(s, a.v_tail + off, a.t_ss, t0, a.tail_len);
+        accumulate_tile(s, oacc);
+        parity ^= 1;
+    }
+    consumer_sync();
+    const long long slot = (long long)bh * a.n_splits + split;
+    if (warp < 8) {
+        const int g0 = 2 * (lane & 3), d0 = warp * 16 + (lane >> 2);
+        if (g0 < G) {
+            a.part_o[(slot * G + g0) * kAD + d0] = oacc[0];
+            a.part_o[(slot * G + g0) * kAD + d0 + 8] = oacc[2];
+        }
+        if (g0 + 1 < G) {
+            a.part_o[(slot * G + g0 + 1) * kAD + d0] = oacc[1];
+            a.part_o[(slot * G + g0 + 1) * kAD + d0 + 8] = oacc[3];
+        }
+    }
+    if (tid < G) {
+        const float m2 = s.m[parity][tid];
+        a.part_ml[(slot * G + tid) * 2 + 0] = m2 == -INFINITY ? -INFINITY : m2 / kLog2e;   // natural-log domain
+        a.part_ml[(slot * G + tid) * 2 + 1] = s.l[tid];
+    }
+}
+
+static_assert(sizeof(AttnPipeSmem) <= 113 * 1024, "two CTAs of the pipelined kernel must fit one SM");
+
+int pick_splits(int B, int Hkv, int items, int D) {
     int sms = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int want = (3 * sms + B * Hkv - 1) / (B * Hkv);     // about three CTAs per SM
+    // one wave: the pipelined kernel keeps two CTAs per SM resident, the plain one three
+    int want = D == kAD ? (2 * sms) / (B * Hkv) : (3 * sms + B * Hkv - 1) / (B * Hkv);
     if (want > items) want = items;
     if (want < 1) want = 1;
     if (want > 64) want = 64;
@@ -346,7 +748,7 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         return ADACODE_ERR_INVALID_ARG;
     const int items = n_segments + (tail_len + kTileTokens - 1) / kTileTokens;
     if (items == 0) return ADACODE_ERR_INVALID_ARG;
-    if (n_splits <= 0) n_splits = pick_splits(B, Hkv, items);
+    if (n_splits <= 0) n_splits = pick_splits(B, Hkv, items, D);
     if (n_splits > 64) n_splits = 64;
     if (workspace_bytes < adacode_decode_attn_workspace_bytes(B, Hq, D, n_splits)) return ADACODE_ERR_WORKSPACE;
     AttnArgs a;
@@ -364,11 +766,32 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
     if (cudaGetDevice(&dev) != cudaSuccess) return ADACODE_ERR_CUDA;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmem)) !=
-            cudaSuccess)
+                cudaSuccess ||
+            cudaFuncSetAttribute(k_decode_attn_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sizeof(AttnPipeSmem)) != cudaSuccess)
             return ADACODE_ERR_CUDA;
         attr_set[dev] = true;
     }
-    k_decode_attn<<<dim3(n_splits, B * Hkv), kAttnThreads, sizeof(AttnSmem), st>>>(a);
+    // head_dim 128: the pipelined tensor-core kernel; ADACODE_ATTN_SIMPLE=1 forces the plain one
+    static const bool force_simple = [] {
+        const char *v = getenv("ADACODE_ATTN_SIMPLE");
+        return v && v[0] == '1';
+    }();
+    if (D == kAD && !force_simple) {
+        AttnPipeArgs pa;
+        pa.a = a;
+        UnpackPipeArgs u;
+        u.sign_mant = nullptr, u.codes = nullptr, u.escapes = nullptr, u.escapes_len = 0;
+        u.tile_base = nullptr, u.seg_off = nullptr, u.left = 0, u.nbits = 0;
+        u.H = Hkv, u.BH = B * Hkv, u.seq_tile = kTileTokens, u.D = D, u.tile_elems = kTileTokens * D;
+        u.n_tiles = (long long)n_segments * B * Hkv;
+        u.dst = nullptr, u.db = 0, u.dh = 0, u.ds = 0, u.status = status;
+        pa.k = u, pa.v = u;
+        pa.k.seg = k_segments_dev, pa.v.seg = v_segments_dev;
+        k_decode_attn_pipe<<<dim3(n_splits, B * Hkv), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
+    } else {
+        k_decode_attn<<<dim3(n_splits, B * Hkv), kAttnThreads, sizeof(AttnSmem), st>>>(a);
+    }
     if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;
     k_decode_attn_combine<<<B * Hq, D, 0, st>>>(a.part_o, a.part_ml, Hq, Hkv, G, D, n_splits, (uint16_t *)out_bf16);
     if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;

@@ -252,6 +252,74 @@ __device__ __forceinline__ TileSrc shfl_tile(const TileSrc &m, int src) {
     return t;
 }
 
+// The part of a tile's escape stream that is staged in shared memory with each of its units.
+// The window [a0, a0 + win) of whole 16-byte granules is fetched with one bulk copy.  It may
+// begin up to 15 bytes before the tile's first escape (same granule, ignored), but never reaches
+// past the last whole granule of the stream: what lies in the stream's final partial granule
+// (`tail` bytes) is fetched with plain loads.
+struct EscWindow {
+    const uint8_t *a0;
+    int win, tail, staged, shift;
+};
+
+__device__ __forceinline__ EscWindow esc_window(const TileSrc &t) {
+    EscWindow w;
+    // stage no more than the stream really holds, so that a short stream is reported as such
+    long long avail = t.esc_len - t.esc_start;
+    if (avail > t.esc_cnt) avail = t.esc_cnt;
+    if (avail > kEscStage) avail = kEscStage;
+    w.staged = avail > 0 ? (int)avail : 0;
+    const uint8_t *ea = t.esc + t.esc_start;
+    w.shift = (int)((uintptr_t)ea & 15);
+    w.a0 = ea - w.shift;
+    w.win = (w.shift + w.staged + 15) & ~15;
+    w.tail = 0;
+    const uintptr_t stream_end = (uintptr_t)(t.esc + t.esc_len);
+    if (w.staged > 0 && (uintptr_t)w.a0 + (uintptr_t)w.win > stream_end) {
+        w.win -= 16;
+        w.tail = (int)(stream_end & 15);
+    }
+    if (w.staged == 0) w.win = 0;
+    return w;
+}
+
+// Producer warp, stage known to be free: describe the unit (rows [row0, row0 + rows) of tile t) in
+// the stage's meta block and start its bulk copies against `full_bar`.
+__device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, const TileSrc &t, const EscWindow &w,
+                                           int row0, int rows, int D, uint16_t *dst, bool first_unit,
+                                           int32_t *status) {
+    const int lane = threadIdx.x & 31;
+    if (w.tail > 0) {
+        if (lane < w.tail) st.esc[w.win + lane] = w.a0[w.win + lane];
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const int elems = rows * D;
+        const uint8_t *src_sm = t.sm + (long long)row0 * D;
+        const uint8_t *src_cd = t.codes + (long long)row0 * D * t.nbits / 8;
+        UnitMeta &m = st.meta;
+        m.dst = dst;
+        m.esc = t.esc, m.esc_len = t.esc_len, m.esc_tile_start = t.esc_start;
+        m.esc_staged = w.staged, m.esc_shift = w.shift;
+        m.elems = elems, m.left = t.left, m.nbits = t.nbits;
+        m.first_unit_of_tile = first_unit;
+        const uint32_t cbytes = (uint32_t)elems * t.nbits / 8;
+        if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)dst) & 15) != 0 || (cbytes & 15) != 0 || t.nbits < 1 ||
+            t.nbits > 4) {
+            // never start a misaligned bulk copy: flag it and hand over an empty unit
+            atomicOr(status, ADACODE_STATUS_MISALIGNED);
+            m.elems = 0;
+            m.nbits = 1;
+            mbar_arrive_expect_tx(full_bar, 0);
+        } else {
+            mbar_arrive_expect_tx(full_bar, (uint32_t)elems + cbytes + (uint32_t)w.win);
+            bulk_load(st.sm, src_sm, (uint32_t)elems, full_bar);
+            bulk_load(st.codes, src_cd, cbytes, full_bar);
+            if (w.win > 0) bulk_load(st.esc, w.a0, (uint32_t)w.win, full_bar);
+        }
+    }
+}
+
 template <int N>
 __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
                                             int &consumed, bool rows_contig, int D, long long ds,
@@ -393,61 +461,14 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
             const int n_here = (int)(my_tiles - base < 32 ? my_tiles - base : 32);
             for (int j = 0; j < n_here; ++j) {
                 const TileSrc t = shfl_tile(mine, j);
-                // stage no more than the stream really holds, so that a short stream is reported as such
-                long long avail = t.esc_len - t.esc_start;
-                if (avail > t.esc_cnt) avail = t.esc_cnt;
-                if (avail > kEscStage) avail = kEscStage;
-                int staged = avail > 0 ? (int)avail : 0;
-                const uint8_t *ea = t.esc + t.esc_start;
-                const int shift = (int)((uintptr_t)ea & 15);
-                // The window [a0, a0 + win) of whole 16-byte granules is fetched with one bulk copy.
-                // It may begin up to 15 bytes before the tile's first escape (same granule, ignored),
-                // but never reaches past the last whole granule of the stream: what lies in the
-                // stream's final partial granule is fetched with plain loads.
-                const uint8_t *a0 = ea - shift;
-                int win = (shift + staged + 15) & ~15;
-                const uintptr_t stream_end = (uintptr_t)(t.esc + t.esc_len);
-                int tail = 0;            // bytes of the final partial granule that this tile needs
-                if (staged > 0 && (uintptr_t)a0 + (uintptr_t)win > stream_end) {
-                    win -= 16;
-                    tail = (int)(stream_end & 15);
-                }
-                if (staged == 0) win = 0;
+                const EscWindow w = esc_window(t);
                 for (int u = 0; u < units_per_tile; ++u, ++it) {
                     const int stg = it % kStages;
-                    UnpackStage &st = s.stage[stg];
                     mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
-                    if (tail > 0) {
-                        if (lane < tail) st.esc[win + lane] = a0[win + lane];
-                        __syncwarp();
-                    }
-                    if (lane == 0) {
-                        const int row0 = u * unit_rows;
-                        const int rows = min(unit_rows, a.seq_tile - row0);
-                        const int elems = rows * a.D;
-                        const uint8_t *src_sm = t.sm + (long long)row0 * a.D;
-                        const uint8_t *src_cd = t.codes + (long long)row0 * a.D * t.nbits / 8;
-                        UnitMeta &m = st.meta;
-                        m.dst = t.dst + (long long)row0 * a.ds;
-                        m.esc = t.esc, m.esc_len = t.esc_len, m.esc_tile_start = t.esc_start;
-                        m.esc_staged = staged, m.esc_shift = shift;
-                        m.elems = elems, m.left = t.left, m.nbits = t.nbits;
-                        m.first_unit_of_tile = (u == 0);
-                        const uint32_t cbytes = (uint32_t)elems * t.nbits / 8;
-                        if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)m.dst) & 15) != 0 || (cbytes & 15) != 0 ||
-                            t.nbits < 1 || t.nbits > 4) {
-                            // never start a misaligned bulk copy: flag it and hand over an empty unit
-                            atomicOr(a.status, ADACODE_STATUS_MISALIGNED);
-                            m.elems = 0;
-                            m.nbits = 1;
-                            mbar_arrive_expect_tx(&s.full[stg], 0);
-                        } else {
-                            mbar_arrive_expect_tx(&s.full[stg], (uint32_t)elems + cbytes + (uint32_t)win);
-                            bulk_load(st.sm, src_sm, (uint32_t)elems, &s.full[stg]);
-                            bulk_load(st.codes, src_cd, cbytes, &s.full[stg]);
-                            if (win > 0) bulk_load(st.esc, a0, (uint32_t)win, &s.full[stg]);
-                        }
-                    }
+                    const int row0 = u * unit_rows;
+                    const int rows = min(unit_rows, a.seq_tile - row0);
+                    issue_unit(s.stage[stg], &s.full[stg], t, w, row0, rows, a.D, t.dst + (long long)row0 * a.ds,
+                               u == 0, a.status);
                 }
             }
         }
@@ -483,6 +504,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
     bulk_wait_all();
 }
 
+#ifndef ADACODE_PIPELINE_UNPACK_ONLY
 // ---------------------------------------------------------------------------------------
 // pack
 // ---------------------------------------------------------------------------------------
@@ -878,3 +900,4 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
         if (total != 0) atomicAdd(hist + tid, total);
     }
 }
+#endif  // ADACODE_PIPELINE_UNPACK_ONLY
