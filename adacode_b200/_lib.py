@@ -26,7 +26,7 @@ EXPORTED_SYMBOLS = (
     'adacode_version', 'adacode_strerror', 'adacode_last_cuda_error', 'adacode_pack_workspace_bytes',
     'adacode_pack_tiles', 'adacode_unpack_tiles', 'adacode_unpack_segments', 'adacode_hist_bf16',
     'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host', 'adacode_pack_tiles_static',
-    'adacode_decode_attn_workspace_bytes', 'adacode_decode_attn',
+    'adacode_decode_attn_workspace_bytes', 'adacode_decode_attn', 'adacode_copy_to_host',
 )
 
 
@@ -87,6 +87,8 @@ def lib() -> ctypes.CDLL:
     L.adacode_decode_attn.restype = i32
     L.adacode_decode_attn.argtypes = [vp, i64, i64, vp, vp, i32, vp, vp, i32, i64, i64, i64,
                                       i32, i32, i32, i32, i32, ctypes.c_float, vp, vp, sz, i32, vp, vp]
+    L.adacode_copy_to_host.restype = i32
+    L.adacode_copy_to_host.argtypes = [vp, vp, sz, vp]
     _lib = L
     return L
 

@@ -33,6 +33,8 @@ class _DeviceScratch:
         self.device = device
         self.workspace = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.mailbox: Optional[torch.Tensor] = None      # pinned host bytes that kernels write results into
+        self.mail_event = torch.cuda.Event()
 
     def workspace_for(self, n_tiles: int, tile_elems: int) -> torch.Tensor:
         need = int(_lib.lib().adacode_pack_workspace_bytes(n_tiles, tile_elems))
@@ -61,10 +63,39 @@ def _stream_ptr(device: torch.device) -> int:
     return int(torch.cuda.current_stream(device).cuda_stream)
 
 
+def read_back(t: torch.Tensor):
+    """Host copy (numpy array of ``t``'s shape and dtype) of a small device tensor.
+
+    The reference reads such values with ``.to('cpu')`` / ``.item()`` (escape totals,
+    compress_tiled_kv.py:559-588; histograms, float_cache_utils.py:373), i.e. with cudaMemcpy, which
+    queues behind whatever bulk transfer occupies the copy engine.  Here a one-CTA kernel stores the
+    bytes into pinned host memory (``adacode_copy_to_host``) and the host waits for an event."""
+    if not t.is_contiguous():
+        t = t.contiguous()
+    nbytes = t.numel() * t.element_size()
+    if nbytes == 0 or nbytes % 4 != 0 or nbytes > (1 << 20):
+        return t.cpu().numpy()
+    dev = t.device
+    sc = _scratch_for(dev)
+    if sc.mailbox is None or sc.mailbox.numel() < nbytes:
+        sc.mailbox = torch.empty(max(1 << 16, nbytes), dtype=torch.uint8).pin_memory()
+    stream = torch.cuda.current_stream(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_copy_to_host(t.data_ptr(), sc.mailbox.data_ptr(), nbytes, int(stream.cuda_stream))
+    if rc == _lib.ERR_INVALID_ARG:
+        return t.cpu().numpy()           # pinned memory this device cannot address: plain copy
+    _lib.check(rc, 'adacode_copy_to_host')
+    sc.mail_event.record(stream)
+    sc.mail_event.synchronize()
+    import numpy as np
+    out = sc.mailbox[:nbytes].numpy().copy()
+    return out.view(np.dtype(str(t.dtype).replace('torch.', ''))).reshape(tuple(t.shape))
+
+
 def check_device_status(device) -> None:
     """Read the device status word (synchronises) and raise if a kernel flagged a problem."""
     s = _scratch_for(torch.device(device))
-    word = int(s.status[0].item())
+    word = int(read_back(s.status)[0])
     if word:
         s.status.zero_()
         problems = []
@@ -275,15 +306,24 @@ def _check_src(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def pack_blocks(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, need_hist: bool = False,
-                hist_out: Optional[torch.Tensor] = None, escape_capacity: Optional[int] = None):
-    """Pack ``x`` [B, H, n_blocks*seq_tile, D] (bf16, any B/H/S strides) into ``n_blocks`` segments
-    with the window ``(right - 2**nbits + 1, right]`` in one launch.
+class _PendingPack:
+    """A pack launch whose escape totals have not been read yet (``pack_blocks_launch``)."""
 
-    Returns ``(PackedChunk, hist)``; ``hist`` is an int32[256] device tensor of all exponents when
-    ``need_hist`` (``hist_out`` is added to instead when given).  One small device-to-host read
-    (segment escape totals and the status word) ends the call.
-    """
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def _default_escape_capacity(n: int) -> int:
+    return min(max(4096, n // 8), max(n, 1))
+
+
+def pack_blocks_launch(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, need_hist: bool = False,
+                       hist_out: Optional[torch.Tensor] = None, escape_capacity: Optional[int] = None,
+                       meta_out: Optional[torch.Tensor] = None) -> _PendingPack:
+    """Start packing ``x`` (see ``pack_blocks``) and return without reading anything back.
+    ``meta_out``: zeroed int64[n_blocks + 2] device buffer for the segment offsets and the status
+    word (e.g. a slice of a buffer that several launches share, so that one ``read_back`` serves
+    them all); the caller passes its host copy to ``pack_blocks_finish``."""
     if nbits not in _SUPPORTED_TILE_NBITS:
         raise ValueError(f'Tiled compressed path supports nbits in {_SUPPORTED_TILE_NBITS}, got {nbits}')
     x = _check_src(x)
@@ -294,55 +334,105 @@ def pack_blocks(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, ne
         raise ValueError(f'sequence length {S} is not a multiple of seq_tile_size {seq_tile}')
     n_blocks = S // seq_tile
     dev = x.device
-    sc = _scratch_for(dev)
     tile_elems = seq_tile * D
-    n_tiles = B * H * n_blocks
-    n = n_tiles * tile_elems
-    L = _lib.lib()
-
-    sign_mant = torch.empty((n_blocks, B * H * tile_elems), dtype=torch.uint8, device=dev)
-    codes = torch.empty((n_blocks, B * H * tile_elems * nbits // 8), dtype=torch.uint8, device=dev)
-    tile_base = torch.empty((n_blocks, B * H), dtype=torch.int32, device=dev)
-    # [segment offsets (n_blocks+1) | status word] in one int64 buffer -> one D2H read
-    meta = torch.zeros(n_blocks + 2, dtype=torch.int64, device=dev)
-    hist = None
+    n = B * H * n_blocks * tile_elems
+    p = _PendingPack(x=x, right=int(right), nbits=int(nbits), seq_tile=seq_tile, B=B, H=H, D=D, n_blocks=n_blocks,
+                     dev=dev, n=n)
+    p.sign_mant = torch.empty((n_blocks, B * H * tile_elems), dtype=torch.uint8, device=dev)
+    p.codes = torch.empty((n_blocks, B * H * tile_elems * nbits // 8), dtype=torch.uint8, device=dev)
+    p.tile_base = torch.empty((n_blocks, B * H), dtype=torch.int32, device=dev)
+    # [segment offsets (n_blocks+1) | status word] in one int64 buffer -> one read
+    p.meta = meta_out if meta_out is not None else torch.zeros(n_blocks + 2, dtype=torch.int64, device=dev)
+    if p.meta.numel() != n_blocks + 2 or p.meta.dtype != torch.int64 or not p.meta.is_contiguous():
+        raise ValueError('meta_out must be a contiguous int64 tensor of n_blocks + 2 entries')
+    p.hist = None
     if need_hist:
-        hist = hist_out if hist_out is not None else torch.zeros(256, dtype=torch.int32, device=dev)
-    cap = int(escape_capacity) if escape_capacity is not None else max(4096, n // 16)
-    cap = min(cap, max(n, 1))
-    ws = sc.workspace_for(n_tiles, tile_elems)
-    status_ptr = meta.data_ptr() + 8 * (n_blocks + 1)
-    sb, sh, ss, _ = x.stride()
+        p.hist = hist_out if hist_out is not None else torch.zeros(256, dtype=torch.int32, device=dev)
+    p.cap = min(int(escape_capacity), max(n, 1)) if escape_capacity is not None else _default_escape_capacity(n)
+    p.escapes = _pack_launch(p, p.cap, p.hist)
+    return p
 
-    def launch(capacity: int, hist_t):
-        esc = torch.empty(capacity, dtype=torch.uint8, device=dev)
-        with torch.cuda.device(dev):
-            rc = L.adacode_pack_tiles(
-                x.data_ptr(), sb, sh, ss, B, H, n_blocks, seq_tile, D, int(right), int(nbits),
-                sign_mant.data_ptr(), codes.data_ptr(), esc.data_ptr(), capacity, tile_base.data_ptr(),
-                meta.data_ptr(), 0 if hist_t is None else hist_t.data_ptr(), ws.data_ptr(), ws.numel(),
-                status_ptr, _stream_ptr(dev))
-        _lib.check(rc, 'adacode_pack_tiles')
-        return esc
 
-    escapes = launch(cap, hist)
-    host = meta.cpu()
-    offsets = [int(v) for v in host[: n_blocks + 1].tolist()]
+def _pack_launch(p: _PendingPack, capacity: int, hist_t) -> torch.Tensor:
+    sc = _scratch_for(p.dev)
+    n_tiles = p.B * p.H * p.n_blocks
+    ws = sc.workspace_for(n_tiles, p.seq_tile * p.D)
+    esc = torch.empty(capacity, dtype=torch.uint8, device=p.dev)
+    sb, sh, ss, _ = p.x.stride()
+    with torch.cuda.device(p.dev):
+        rc = _lib.lib().adacode_pack_tiles(
+            p.x.data_ptr(), sb, sh, ss, p.B, p.H, p.n_blocks, p.seq_tile, p.D, p.right, p.nbits,
+            p.sign_mant.data_ptr(), p.codes.data_ptr(), esc.data_ptr(), capacity, p.tile_base.data_ptr(),
+            p.meta.data_ptr(), 0 if hist_t is None else hist_t.data_ptr(), ws.data_ptr(), ws.numel(),
+            p.meta.data_ptr() + 8 * (p.n_blocks + 1), _stream_ptr(p.dev))
+    _lib.check(rc, 'adacode_pack_tiles')
+    return esc
+
+
+def pack_blocks_finish(p: _PendingPack, host_meta):
+    """Finish a launch given the host copy of its ``meta`` (int64[n_blocks + 2]): re-run with the
+    exact capacity if the escape buffer was too small, trim it, build the ``PackedChunk``."""
+    n_blocks = p.n_blocks
+    offsets = [int(v) for v in host_meta[: n_blocks + 1]]
     total = offsets[-1]
-    status = int(host[n_blocks + 1].item()) & 0xFFFFFFFF
-    if total > cap or (status & _lib.STATUS_ESCAPE_OVERFLOW):
-        meta.zero_()
-        escapes = launch(total, None)   # histogram already complete from the first pass
-        host = meta.cpu()
-        if int(host[n_blocks + 1].item()) & 0xFFFFFFFF:
+    status = int(host_meta[n_blocks + 1]) & 0xFFFFFFFF
+    escapes = p.escapes
+    if total > p.cap or (status & _lib.STATUS_ESCAPE_OVERFLOW):
+        p.meta.zero_()
+        escapes = _pack_launch(p, total, None)   # histogram already complete from the first pass
+        host = read_back(p.meta)
+        if int(host[n_blocks + 1]) & 0xFFFFFFFF:
             raise _lib.AdacodeError('adacode_pack_tiles: escape overflow after re-run with exact capacity')
+    elif status:
+        raise _lib.AdacodeError(f'adacode_pack_tiles: device status {status:#x}')
     if escapes.numel() > 2 * total + 65536:
         escapes = escapes[:total].clone()
     else:
         escapes = escapes[:total]
-    chunk = PackedChunk(sign_mant, codes, escapes, tile_base, offsets, meta[: n_blocks + 1], int(right) - 2 ** int(nbits) + 1,
-                        int(right), int(nbits), B, H, seq_tile, D)
-    return chunk, hist
+    chunk = PackedChunk(p.sign_mant, p.codes, escapes, p.tile_base, offsets, p.meta[: n_blocks + 1],
+                        p.right - 2 ** p.nbits + 1, p.right, p.nbits, p.B, p.H, p.seq_tile, p.D)
+    return chunk, p.hist
+
+
+def pack_blocks(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, need_hist: bool = False,
+                hist_out: Optional[torch.Tensor] = None, escape_capacity: Optional[int] = None):
+    """Pack ``x`` [B, H, n_blocks*seq_tile, D] (bf16, any B/H/S strides) into ``n_blocks`` segments
+    with the window ``(right - 2**nbits + 1, right]`` in one launch.
+
+    Returns ``(PackedChunk, hist)``; ``hist`` is an int32[256] device tensor of all exponents when
+    ``need_hist`` (``hist_out`` is added to instead when given).  One small device-to-host read
+    (segment escape totals and the status word) ends the call.
+    """
+    p = pack_blocks_launch(x, right, nbits, seq_tile, need_hist, hist_out, escape_capacity)
+    return pack_blocks_finish(p, read_back(p.meta))
+
+
+def pack_pair(k: torch.Tensor, v: torch.Tensor, k_params, v_params, seq_tile: int = 128, need_hist: bool = False,
+              capacities=(None, None)):
+    """Pack the keys and the values of one span with one round trip to the host: both launches
+    write their segment offsets, status words and (with ``need_hist``) exponent histograms into
+    one device buffer that a single ``read_back`` fetches.  Returns
+    ``(k_chunk, v_chunk, k_hist, v_hist, k_hist_host, v_hist_host)``; the ``*_host`` entries are
+    numpy int32[256] copies of the histograms (None without ``need_hist``)."""
+    dev = k.device
+    nk = k.shape[-2] // seq_tile + 2
+    nv = v.shape[-2] // seq_tile + 2
+    words = nk + nv + (256 if need_hist else 0)          # int64 words; two int32[256] histograms = 256 words
+    mail = torch.zeros(words, dtype=torch.int64, device=dev)
+    k_hist = v_hist = None
+    if need_hist:
+        h = mail[nk + nv:].view(torch.int32)
+        k_hist, v_hist = h[:256], h[256:]
+    pk = pack_blocks_launch(k, k_params[0], k_params[1], seq_tile, need_hist, k_hist, capacities[0], mail[:nk])
+    pv = pack_blocks_launch(v, v_params[0], v_params[1], seq_tile, need_hist, v_hist, capacities[1], mail[nk:nk + nv])
+    host = read_back(mail)
+    k_chunk, _ = pack_blocks_finish(pk, host[:nk])
+    v_chunk, _ = pack_blocks_finish(pv, host[nk:nk + nv])
+    kh = vh = None
+    if need_hist:
+        hh = host[nk + nv:].view('int32')
+        kh, vh = hh[:256].copy(), hh[256:].copy()
+    return k_chunk, v_chunk, k_hist, v_hist, kh, vh
 
 
 def unpack_chunk(chunk: PackedChunk, dst: torch.Tensor, seq_offset: int = 0) -> None:

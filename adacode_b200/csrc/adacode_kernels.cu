@@ -690,6 +690,13 @@ void launch_pack(const PackArgs &a, int grid, cudaStream_t st) {
     else k_pack<N, CH, false><<<grid, kThreads, 0, st>>>(a);
 }
 
+// Word-wise copy of a small device buffer into host memory that the device can address (pinned
+// memory under unified addressing); one CTA.
+__global__ void k_copy_to_host(const uint32_t *__restrict__ src, uint32_t *dst, size_t words) {
+    for (size_t i = threadIdx.x; i < words; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
@@ -713,6 +720,21 @@ const char *adacode_strerror(int code) {
 }
 
 const char *adacode_last_cuda_error(void) { return g_last_cuda_error; }
+
+int adacode_copy_to_host(const void *src_dev, void *dst_host_pinned, size_t bytes, void *stream) {
+    if (bytes == 0) return ADACODE_OK;
+    if (!src_dev || !dst_host_pinned || (bytes & 3) != 0 || (((uintptr_t)src_dev | (uintptr_t)dst_host_pinned) & 3) != 0)
+        return ADACODE_ERR_INVALID_ARG;
+    if (bytes > (1u << 20)) return ADACODE_ERR_TOO_LARGE;
+    cudaPointerAttributes attr;
+    ADACODE_CUDA_TRY(cudaPointerGetAttributes(&attr, dst_host_pinned));
+    // only page-locked host memory that this device can address; anything else is refused, not tried
+    if (attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) return ADACODE_ERR_INVALID_ARG;
+    k_copy_to_host<<<1, 256, 0, (cudaStream_t)stream>>>((const uint32_t *)src_dev, (uint32_t *)attr.devicePointer,
+                                                       bytes / 4);
+    ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
+}
 
 size_t adacode_pack_workspace_bytes(int64_t n_tiles, int64_t tile_elems) {
     if (n_tiles <= 0 || tile_elems <= 0) return 256;

@@ -216,6 +216,8 @@ class float11Layer(DynamicLayer):
         # optional callable applied to every histogram before the adjuster reads it (sharded caches
         # sum the histograms of all shards here)
         self.hist_reduce = None
+        self._escape_fraction = (None, None)   # of the last packed span, keys and values
+        self._host_hists = None                # (device K hist, host copy, device V hist, host copy) of the last pack
 
     # ------------------------------------------------------------------ reference-named views
     @property
@@ -251,6 +253,7 @@ class float11Layer(DynamicLayer):
         state['hist_reduce'] = None          # process groups do not pickle
         state['_mirror'] = {}
         state['_mirror_valid'] = {'k': 0, 'v': 0}
+        state['_host_hists'] = None
         state['_cache_view_static'] = None
         state['_cache_view_runtime'] = None
         return state
@@ -281,8 +284,9 @@ class float11Layer(DynamicLayer):
         v_hist = self._extract_exponent_histogram(value_states)
         if k_hist is None or v_hist is None:
             raise RuntimeError('Unable to initialize compression parameters from empty KV tensors.')
-        self._set_compress_params(codec.analysis_best_bits(k_hist.to('cpu')),
-                                  codec.analysis_best_bits(v_hist.to('cpu')), count_as_auto_init=True)
+        both = codec.read_back(torch.stack([k_hist.to(torch.int32), v_hist.to(torch.int32)]))
+        self._set_compress_params(codec.analysis_best_bits(both[0]), codec.analysis_best_bits(both[1]),
+                                  count_as_auto_init=True)
 
     def _record_adjust_proposal(self, new_keys_params, new_values_params) -> None:
         """reference: :624-641 — a proposal counts when it differs from the previous proposal."""
@@ -359,10 +363,15 @@ class float11Layer(DynamicLayer):
             raise ValueError(
                 'Tiled compressed path currently requires seq_tile_size == seq_len per compressed block, '
                 f'got seq_tile_size={self.seq_tile_size}, seq_len={self.block_size}')
-        k_chunk, k_hist = codec.pack_blocks(key_states, self.keys_right, self.keys_nbits, self.seq_tile_size,
-                                            need_hist=need_adjust)
-        v_chunk, v_hist = codec.pack_blocks(value_states, self.values_right, self.values_nbits,
-                                            self.seq_tile_size, need_hist=need_adjust)
+        # keys and values are launched back to back and share one read of their escape totals, status
+        # words and histograms; the escape buffers are sized from what this layer's last span needed
+        nk, nv = key_states.numel(), value_states.numel()
+        caps = tuple(None if f is None else int(n * f * 1.25) + 4096 for n, f in zip((nk, nv), self._escape_fraction))
+        k_chunk, v_chunk, k_hist, v_hist, kh_host, vh_host = codec.pack_pair(
+            key_states, value_states, (self.keys_right, self.keys_nbits), (self.values_right, self.values_nbits),
+            self.seq_tile_size, need_hist=need_adjust, capacities=caps)
+        self._escape_fraction = (k_chunk.n_escapes / max(nk, 1), v_chunk.n_escapes / max(nv, 1))
+        self._host_hists = (k_hist, kh_host, v_hist, vh_host) if need_adjust else None
         self._key_segments.extend(k_chunk.segments())
         self._value_segments.extend(v_chunk.segments())
         n_blocks = k_chunk.n_blocks
@@ -448,8 +457,15 @@ class float11Layer(DynamicLayer):
         if self.hist_reduce is not None:
             keys_exp_count = self.hist_reduce(keys_exp_count)
             values_exp_count = self.hist_reduce(values_exp_count)
-        new_keys = codec.analysis_best_bits(keys_exp_count.to('cpu'))
-        new_values = codec.analysis_best_bits(values_exp_count.to('cpu'))
+        cached = self._host_hists
+        if cached is not None and self.hist_reduce is None and cached[0] is keys_exp_count and cached[2] is values_exp_count:
+            k_host, v_host = cached[1], cached[3]        # came back with the pack's own read
+        else:
+            both = codec.read_back(torch.stack([keys_exp_count.to(torch.int32), values_exp_count.to(torch.int32)]))
+            k_host, v_host = both[0], both[1]
+        self._host_hists = None
+        new_keys = codec.analysis_best_bits(k_host)
+        new_values = codec.analysis_best_bits(v_host)
         if not self.compress_params_initialized:
             if not self.auto_init_compress_params:
                 raise RuntimeError('Compression parameters are not initialized.')

@@ -406,7 +406,7 @@ class MLAFloat11Cache(Float11Cache):
             if layer.hist_reduce is not None:
                 keys_exp_count = layer.hist_reduce(keys_exp_count)
             try:
-                self._pending_adjusts[layer_idx] = ('ok', codec.analysis_best_bits(keys_exp_count.to('cpu')))
+                self._pending_adjusts[layer_idx] = ('ok', codec.analysis_best_bits(codec.read_back(keys_exp_count.to(torch.int32))))
             except IndexError as exc:
                 self._pending_adjusts[layer_idx] = ('err', exc)
         if layer_idx == len(self.layers) - 1:

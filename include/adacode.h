@@ -197,6 +197,20 @@ int adacode_choose_params_host(const int64_t *hist256, int *right, int *nbits);
 int adacode_calibrate_host(const int64_t *hist256, int *right, int *nbits);
 
 /*
+ * Copy `bytes` (a multiple of 4, at most 1 MiB) from device memory into page-locked host memory
+ * with a kernel, in stream order; the caller waits for an event recorded after it and reads the
+ * host buffer.  dst must be pinned host memory that the current device can address (cudaHostAlloc /
+ * cudaHostRegister under unified addressing): anything else is refused with
+ * ADACODE_ERR_INVALID_ARG, nothing is launched.
+ * Replaces: the small `.to('cpu')` / `.item()` reads of the reference's cache (escape totals of a
+ *   freshly packed block, compress_tiled_kv.py:559-588; adjuster histograms,
+ *   float_cache_utils.py:373, :883-891).  Those are cudaMemcpy calls: on a GPU whose copy engine is
+ *   busy with bulk transfers (KV offload, prefill upload) each of them queues behind megabytes of
+ *   unrelated traffic.  A kernel's stores to mapped memory do not use the copy engine.
+ */
+int adacode_copy_to_host(const void *src_dev, void *dst_host_pinned, size_t bytes, void *stream);
+
+/*
  * Bytes of scratch adacode_decode_attn needs (split partials, fp32).  n_splits <= 0 sizes for
  * the largest split count the library will pick itself.
  */
@@ -216,8 +230,9 @@ size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);
  *   decode_impl 'materialize_dense' (float_cache_utils.py:1342) and always rebuild dense K/V
  *   (float11Layer.update, :1278-1316) before the model's own attention runs; the module its
  *   validation script imports for a fused path (ops/kv_attention.py) is not in its tree.
- * Arithmetic: products and sums in fp32, probabilities kept in fp32, output rounded to bf16
- * (nearest even).  Requirements: seq_tile == 128, D in {64, 128}, G <= 8, q with unit stride
+ * Arithmetic: products and sums in fp32 (head_dim 128: bf16 x bf16 tensor-core products with
+ * fp32 accumulation, probabilities rounded to bf16 for the weighted sum and its denominator
+ * alike; head_dim 64: fp32 throughout), output rounded to bf16 (nearest even).  Requirements: seq_tile == 128, D in {64, 128}, G <= 8, q with unit stride
  * along D and element strides q_stride_b/h, out contiguous [B][Hq][D].
  */
 int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride_h,

@@ -86,3 +86,15 @@ def exponent_hist(x, hist_out=None):
 
 def analysis_best_bits(data_freq, store_index=False):
     return O.choose_params(np.asarray(data_freq.tolist() if hasattr(data_freq, 'tolist') else data_freq, np.int64))
+
+
+def pack_pair(k, v, k_params, v_params, seq_tile=128, need_hist=False, capacities=(None, None)):
+    k_chunk, k_hist = pack_blocks(k, k_params[0], k_params[1], seq_tile, need_hist)
+    v_chunk, v_hist = pack_blocks(v, v_params[0], v_params[1], seq_tile, need_hist)
+    kh = k_hist.numpy().copy() if need_hist else None
+    vh = v_hist.numpy().copy() if need_hist else None
+    return k_chunk, v_chunk, k_hist, v_hist, kh, vh
+
+
+def read_back(t):
+    return t.cpu().numpy()

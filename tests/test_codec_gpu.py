@@ -177,3 +177,33 @@ def test_argument_errors(cuda_device):
         codec.compress_tiled_tensor(x, right=129, nbits=3, seq_tile_size=64)
     with pytest.raises(Exception):
         codec.pack_blocks(x.cpu(), 129, 3)
+
+
+def test_read_back_matches_cpu_copy(cuda_device):
+    """The kernel-written host mailbox returns exactly what a plain device-to-host copy returns."""
+    from adacode_b200 import codec
+    g = torch.Generator('cpu').manual_seed(3)
+    for dtype, shape in ((torch.int64, (163,)), (torch.int32, (2, 256)), (torch.int32, (1,)), (torch.uint8, (64,))):
+        t = torch.randint(0, 100, shape, generator=g).to(dtype).to(cuda_device)
+        got = codec.read_back(t)
+        assert got.shape == tuple(shape) and np.array_equal(got, t.cpu().numpy())
+    odd = torch.arange(7, dtype=torch.uint8, device=cuda_device)        # not a multiple of 4 bytes: plain copy
+    assert np.array_equal(codec.read_back(odd), odd.cpu().numpy())
+
+
+def test_pack_pair_equals_two_packs(cuda_device):
+    """Keys and values packed with one shared read give the same chunks and histograms as two
+    separate ``pack_blocks`` calls, also when the suggested escape capacity is far too small."""
+    from adacode_b200 import codec
+    k = synth.kv_tensor((2, 4, 384, 128), seed=31, key_offset=True).to(cuda_device)
+    v = synth.kv_tensor((2, 4, 384, 128), seed=32).to(cuda_device)
+    for caps in ((None, None), (16, 16)):
+        kc, vc, kh, vh, kh_host, vh_host = codec.pack_pair(k, v, (129, 3), (127, 2), 128, need_hist=True, capacities=caps)
+        for x, chunk, hist, hist_host, (right, nbits) in ((k, kc, kh, kh_host, (129, 3)), (v, vc, vh, vh_host, (127, 2))):
+            ref, ref_hist = codec.pack_blocks(x, right, nbits, 128, need_hist=True)
+            assert chunk.seg_offsets == ref.seg_offsets
+            for a, b in ((chunk.sign_mant, ref.sign_mant), (chunk.codes, ref.codes), (chunk.escapes, ref.escapes),
+                         (chunk.tile_base, ref.tile_base), (hist, ref_hist)):
+                assert torch.equal(a, b)
+            assert np.array_equal(hist_host, ref_hist.cpu().numpy())
+    codec.check_device_status(cuda_device)
