@@ -6,9 +6,10 @@ them.  For a single new token that moves, per cached element, the packed bytes i
 bytes out and two dense bytes in again.  The kernel behind this module reads the packed planes
 once and never writes dense K/V.
 
-The result is fp32 attention over the exact (lossless) cache, rounded to bf16; it is *not*
-bit-identical to what a model's stock attention kernel produces from the same dense K/V,
-because the order of the fp32 sums differs.  Token-for-token equality with an uncompressed
+The result is attention over the exact (lossless) cache with fp32 accumulation (for head_dim 128
+the products run on the tensor cores and the probabilities are rounded to bf16 first), rounded
+to bf16; it is *not* bit-identical to what a model's stock attention kernel produces from the
+same dense K/V, because the order of the fp32 sums differs.  Token-for-token equality with an uncompressed
 cache is only promised by the materialising path (``Float11Cache.update``).
 """
 from __future__ import annotations
@@ -22,7 +23,7 @@ from . import _lib
 from .codec import _scratch_for, _stream_ptr, build_segment_table
 
 _SEQ_TILE = 128
-_MAX_SPLITS = 64
+_MAX_SPLITS = 128
 
 _workspaces: dict = {}
 

@@ -710,16 +710,29 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
 
 static_assert(sizeof(AttnPipeSmem) <= 113 * 1024, "two CTAs of the pipelined kernel must fit one SM");
 
+constexpr int kMaxSplits = 128;
+
+// Splits per (batch, KV head): the grid should fill a whole number of waves of resident CTAs
+// (two per SM for the pipelined kernel, three for the plain one).  One, two and three waves are
+// tried and the fullest wins; fewer waves on ties (more tiles per CTA, less per-CTA overhead).
 int pick_splits(int B, int Hkv, int items, int D) {
     int sms = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // one wave: the pipelined kernel keeps two CTAs per SM resident, the plain one three
-    int want = D == kAD ? (2 * sms) / (B * Hkv) : (3 * sms + B * Hkv - 1) / (B * Hkv);
-    if (want > items) want = items;
-    if (want < 1) want = 1;
-    if (want > 64) want = 64;
-    return want;
+    const long long slots = (long long)sms * (D == kAD ? 2 : 3);
+    const long long bh = (long long)B * Hkv;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int waves = 1; waves <= 3; ++waves) {
+        long long sp = waves * slots / bh;
+        if (sp < 1) sp = 1;
+        if (sp > items) sp = items;
+        if (sp > kMaxSplits) sp = kMaxSplits;
+        const long long ctas = bh * sp;
+        const double fill = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+        if (fill > best_fill + 0.02) best_fill = fill, best = (int)sp;
+    }
+    return best;
 }
 
 }  // namespace
@@ -728,7 +741,7 @@ extern "C" {
 
 size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits) {
     if (B <= 0 || Hq <= 0 || D <= 0) return 0;
-    if (n_splits <= 0) n_splits = 64;
+    if (n_splits <= 0 || n_splits > kMaxSplits) n_splits = kMaxSplits;
     return (size_t)B * Hq * n_splits * ((size_t)D + 2) * sizeof(float);
 }
 
@@ -749,7 +762,7 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
     const int items = n_segments + (tail_len + kTileTokens - 1) / kTileTokens;
     if (items == 0) return ADACODE_ERR_INVALID_ARG;
     if (n_splits <= 0) n_splits = pick_splits(B, Hkv, items, D);
-    if (n_splits > 64) n_splits = 64;
+    if (n_splits > kMaxSplits) n_splits = kMaxSplits;
     if (workspace_bytes < adacode_decode_attn_workspace_bytes(B, Hq, D, n_splits)) return ADACODE_ERR_WORKSPACE;
     AttnArgs a;
     a.q = (const uint16_t *)q_bf16, a.q_sb = q_stride_b, a.q_sh = q_stride_h;

@@ -3,7 +3,8 @@
 ``python -m adacode_b200.microbench --shape 16,8,8192,128 --nbits 4 --right 131 --iters 5``
 
 Packs a seeded synthetic K tensor [B, H, S, D] (all S/128 blocks in one launch) and unpacks it
-again, timing each kernel with CUDA events on the launching stream, and prints one line per
+again, timing each kernel with CUDA events on the launching stream (several launches back to
+back per sample, so that host launch latency is not counted), and prints one line per
 kernel with the algorithmic HBM bytes (2 read + 1 + nbits/8 + p written per element for pack,
 the mirror image for unpack, p = escape fraction) divided by the time.  Inputs are larger
 than L2 when the shape is; nothing is copied from or to the host inside the timed region.
@@ -32,18 +33,24 @@ def synthetic_keys(shape, seed: int = 0, device='cuda') -> torch.Tensor:
     return x.repeat(B, 1, reps, 1)[:, :, :S].contiguous()
 
 
-def _time(fn, iters: int, warmup: int) -> float:
+def _time(fn, iters: int, warmup: int, inner: int = 8) -> float:
+    """Median over ``iters`` samples of the device time of one call of ``fn``.  Each sample times
+    ``inner`` calls issued back to back between two events: the host needs tens of microseconds
+    to get through the Python and ctypes layers, which a single call between two events would
+    count as kernel time (the GPU idles until the launch arrives)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     times = []
     for _ in range(iters):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()                      # keeps the queue non-empty while the first timed call is prepared
         a.record()
-        fn()
+        for _ in range(inner):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        times.append(a.elapsed_time(b) / inner)
     times.sort()
     return times[len(times) // 2] * 1e-3
 

@@ -224,7 +224,7 @@ size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);
  * tokens (the cache's not-yet-packed residual, element strides tail_stride_b/h/s, unit
  * stride along D).  Every cached token is visible to the query (no mask).  The planes are
  * decoded tile by tile in shared memory, so HBM sees the packed bytes only; the work is
- * split along the sequence into n_splits parts (<= 0: chosen by the library, at most 64)
+ * split along the sequence into n_splits parts (<= 0: chosen by the library; at most 128)
  * whose partial results a second kernel merges.
  * The reference implementation has no counterpart: its caches report
  *   decode_impl 'materialize_dense' (float_cache_utils.py:1342) and always rebuild dense K/V
