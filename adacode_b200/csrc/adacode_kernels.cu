@@ -801,10 +801,16 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
         pa.status = status;
         int rc = launch_pack_pipe(pa, nbits, st);
         if (rc != ADACODE_OK) return rc;
-        k_compact_units<<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
-                                                    seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
-                                                    pa.unit_rows * D, pa.units_per_tile, escapes, escapes_capacity,
-                                                    hist256, status);
+        if (hist256)
+            k_compact_units<true><<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
+                                                              seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
+                                                              pa.unit_rows * D, pa.units_per_tile, escapes,
+                                                              escapes_capacity, hist256, status);
+        else
+            k_compact_units<false><<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
+                                                               seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
+                                                               pa.unit_rows * D, pa.units_per_tile, escapes,
+                                                               escapes_capacity, nullptr, status);
         ADACODE_CUDA_TRY(cudaGetLastError());
         return ADACODE_OK;
     }

@@ -675,7 +675,7 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
             const uint32_t e4 = ((hi4 & 0x7F7F7F7Fu) << 1) | ((lo4 >> 7) & 0x01010101u);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t code = s.lut[(e4 >> (8 * j)) & 0xFFu];     // 0 when out of the window
+                const uint32_t code = s.lut[__byte_perm(e4, 0u, 0x4440 | j)];     // byte j of e4; 0 when out of the window
                 const int el = 4 * q + j;
                 gg[el >> 3] = code * (1u << ((7 - (el & 7)) * N)) + gg[el >> 3];
             }
@@ -845,8 +845,14 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
 
 // Gather every unit's escape bytes from its scratch slot into the compact per-segment stream.
 // Tile t of segment j starts at seg_off[j] + tile_base[t] - count[t]; its units follow each other.
-// With `hist` set, the escaped exponents are also counted here (full warps of escape bytes, one
-// shared-memory bin array per warp) rather than one by one inside the pack kernel.
+// One warp per tile.  All of a tile's metadata is fetched with independent loads (one memory round
+// trip), the bytes move as aligned 32-bit words (the source words are funnel-shifted into the
+// alignment of the destination; only the first and last word of a run use byte stores).
+// With HIST the escaped exponents are counted here (whole warps of escape bytes) rather than one
+// by one inside the pack kernel.  Escaped exponents cluster on a few values, so each warp keeps
+// four copies of the 256 bins (picked by lane & 3): one copy would serialise most of a warp's
+// shared-memory atomics.
+template <bool HIST>
 __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__restrict__ scratch,
                                                              const int32_t *__restrict__ tile_counts,
                                                              const int32_t *__restrict__ unit_counts,
@@ -855,43 +861,65 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
                                                              int BH, int tile_elems, int unit_elems, int upt,
                                                              uint8_t *__restrict__ escapes, int64_t capacity,
                                                              int32_t *__restrict__ hist, int32_t *status) {
-    // per warp four copies of the 256 bins (picked by lane & 3): escaped exponents cluster on a few
-    // values, so one copy would serialise most of a warp's shared atomics
-    __shared__ int s_hist[kWarps][4][256];
+    __shared__ int s_hist[HIST ? kWarps : 1][HIST ? 4 : 1][HIST ? 256 : 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (hist) {
+    if (HIST) {
         for (int i = tid; i < kWarps * 4 * 256; i += kThreads) (&s_hist[0][0][0])[i] = 0;
         __syncthreads();
     }
-    int *my_hist = &s_hist[warp][lane & 3][0];
+    int *my_hist = &s_hist[HIST ? warp : 0][HIST ? (lane & 3) : 0][0];
     const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t n_warps = (int64_t)gridDim.x * kWarps;
     for (int64_t t = warp_global; t < n_tiles; t += n_warps) {
-        const int c = tile_counts[t];
+        // independent loads: one round trip
+        const int c = __ldg(tile_counts + t);
+        const int tb = __ldg(tile_base + t);
+        const int64_t so = __ldg(seg_off + t / BH);
+        int cu = __ldg(unit_counts + t * upt);
         if (c == 0) continue;
-        int64_t dst = seg_off[t / BH] + tile_base[t] - c;
+        int64_t dst = so + tb - c;
         const bool fits = dst >= 0 && dst + c <= capacity;
         if (!fits && lane == 0) atomicOr(status, ADACODE_STATUS_ESCAPE_OVERFLOW);
         for (int u = 0; u < upt; ++u) {
-            const int cu = unit_counts[t * upt + u];
-            // unit slots start on 16-byte boundaries: read four escape bytes per lane and step
+            if (u > 0) cu = __ldg(unit_counts + t * upt + u);
+            // unit slots start on 16-byte boundaries
             const uint32_t *src4 = reinterpret_cast<const uint32_t *>(scratch + t * tile_elems + (int64_t)u * unit_elems);
-            for (int i = lane * 4; i < cu; i += 128) {
-                uint32_t v = src4[i >> 2];
+            uint8_t *d8 = escapes + dst;
+            const int r = (int)((uintptr_t)d8 & 3);
+            uint32_t *dst32 = reinterpret_cast<uint32_t *>(d8 - r);
+            const int n_words = (r + cu + 3) >> 2;             // destination words touched
+#pragma unroll 2
+            for (int j = lane; j < n_words; j += 32) {
+                const int s0 = 4 * j - r;                      // source index of the byte that lands in byte 0 of word j
+                const uint32_t hi = 4 * j < cu ? src4[j] : 0u;
+                uint32_t v = hi;
+                if (r != 0) {
+                    const uint32_t lo = j > 0 ? src4[j - 1] : 0u;
+                    v = __funnelshift_r(lo, hi, 8 * (4 - r));
+                }
+                if (fits) {
+                    if (s0 >= 0 && s0 + 4 <= cu) {
+                        dst32[j] = v;
+                    } else {
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    if (i + b < cu) {
-                        const uint32_t e = v & 0xFFu;
-                        if (fits) escapes[dst + i + b] = (uint8_t)e;
-                        if (hist) atomicAdd(my_hist + e, 1);
+                        for (int b = 0; b < 4; ++b)
+                            if (s0 + b >= 0 && s0 + b < cu) reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
                     }
-                    v >>= 8;
+                }
+                if (HIST) {
+                    // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
+                    uint32_t w = hi;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        if (4 * j + b < cu) atomicAdd(my_hist + (w & 0xFFu), 1);
+                        w >>= 8;
+                    }
                 }
             }
             dst += cu;
         }
     }
-    if (hist) {
+    if (HIST) {
         __syncthreads();
         int total = 0;
 #pragma unroll
@@ -900,4 +928,5 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
         if (total != 0) atomicAdd(hist + tid, total);
     }
 }
+
 #endif  // ADACODE_PIPELINE_UNPACK_ONLY

@@ -381,12 +381,17 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize(dev)
         return cache
 
-    e2e_step()
+    # a step hands its cache back before the next one starts (a server recycles its cache pool):
+    # otherwise two 36-layer caches are alive at once and every step pays fresh cudaMalloc calls
+    cache = e2e_step()
+    cache.synchronize_and_release()
+    cache = e2e_step()
     barrier()
     w0 = torch.cuda.Event(enable_timing=True)
     w1 = torch.cuda.Event(enable_timing=True)
     w0.record()
     for _ in range(e2e_steps):
+        cache.synchronize_and_release()
         cache = e2e_step()
     w1.record()
     barrier()
@@ -394,6 +399,38 @@ def run_gpu_arm(args) -> None:
     assert torch.equal(host_out[1].view(torch.int16), host_in[-1].view(torch.int16)), 'e2e round trip not bit-exact'
     mem = cache.get_memory()
     ratio = mem['kv_compressed_memory'] / mem['kv_original_memory']
+
+    # ---- optional fused path: one decode step of attention over layer 0 of that cache --------------
+    # (32 query heads on 8 KV heads, every cached token attended to), against unpacking K and V and
+    # running torch SDPA on the dense tensors; several launches back to back per sample
+    import torch.nn.functional as F
+    layer0 = cache.layers[0]
+    q = (torch.randn(1, 32, 1, HEAD_DIM, device=dev) * 0.3).to(torch.bfloat16)
+    dk = torch.empty((1, KV_HEADS, PROMPT, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    dv = torch.empty_like(dk)
+
+    def attn_fused():
+        return layer0.decode_attention(q)
+
+    def attn_materialised():
+        codec.unpack_segments(layer0._key_segments, dk, table=layer0._segment_table('k', layer0._key_segments))
+        codec.unpack_segments(layer0._value_segments, dv, table=layer0._segment_table('v', layer0._value_segments))
+        return F.scaled_dot_product_attention(q, dk, dv, enable_gqa=True)
+
+    def time_us(fn, inner=16):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        a.record()
+        for _ in range(inner):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) * 1e3 / inner
+
+    attn_diff = (attn_fused().float() - attn_materialised().float()).abs().max().item()
+    attn_us = (time_us(attn_fused), time_us(attn_materialised))
 
     times = torch.tensor([total_ms, pack_ms, unpack_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -437,6 +474,9 @@ def run_gpu_arm(args) -> None:
             'e2e': {'value': round(world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9, 2), 'unit': 'GB/s',
                     'h2d_bytes_per_step': int(bf16_bytes), 'd2h_bytes_per_step': int(bf16_bytes),
                     'ms_per_step': round(e2e_ms, 2), 'api': 'Float11Cache.update + materialize_layer'},
+            'decode_attention': {'shape': f'q [1,32,1,{HEAD_DIM}] over one layer of the cache ({PROMPT} tokens)',
+                                 'fused_us': round(attn_us[0], 1), 'unpack_then_sdpa_us': round(attn_us[1], 1),
+                                 'max_abs_diff': round(attn_diff, 5)},
             'gpu_launches': args.steps * len(slots) * 3,
             'clocks': clocks,
         }
