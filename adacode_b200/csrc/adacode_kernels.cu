@@ -788,9 +788,10 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
     a.n_blocks = n_blocks;
     a.hist = hist256;
 
-    const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 8
+    // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
+    const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 4
                                 ? (n_tiles + kWarps - 1) / kWarps
-                                : (int64_t)sm_count() * 8);
+                                : (int64_t)sm_count() * 4);
     // (the pipelined kernel counts histogram hits in 16-bit fields per thread: keep tiles below 2**24 elements)
     if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D) && tile_elems <= (1 << 24)) {
         PackPipeArgs pa;

@@ -888,31 +888,38 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
             const int r = (int)((uintptr_t)d8 & 3);
             uint32_t *dst32 = reinterpret_cast<uint32_t *>(d8 - r);
             const int n_words = (r + cu + 3) >> 2;             // destination words touched
+            // four destination words (16 bytes) per lane and step: one 16-byte load of the source
+            // words behind them plus the word before (for the shift)
+            const uint4 *src16 = reinterpret_cast<const uint4 *>(src4);
+            const int n_quads = (n_words + 3) >> 2;
 #pragma unroll 2
-            for (int j = lane; j < n_words; j += 32) {
-                const int s0 = 4 * j - r;                      // source index of the byte that lands in byte 0 of word j
-                const uint32_t hi = 4 * j < cu ? src4[j] : 0u;
-                uint32_t v = hi;
-                if (r != 0) {
-                    const uint32_t lo = j > 0 ? src4[j - 1] : 0u;
-                    v = __funnelshift_r(lo, hi, 8 * (4 - r));
-                }
-                if (fits) {
-                    if (s0 >= 0 && s0 + 4 <= cu) {
-                        dst32[j] = v;
-                    } else {
+            for (int q = lane; q < n_quads; q += 32) {
+                const uint4 cur = 16 * q < cu ? src16[q] : make_uint4(0u, 0u, 0u, 0u);
+                const uint32_t prev = (r != 0 && q > 0) ? src4[4 * q - 1] : 0u;
+                const uint32_t w[5] = {prev, cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
-                        for (int b = 0; b < 4; ++b)
-                            if (s0 + b >= 0 && s0 + b < cu) reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
+                for (int k = 0; k < 4; ++k) {
+                    const int j = 4 * q + k;                       // destination word
+                    const int s0 = 4 * j - r;                      // source index of the byte that lands in its byte 0
+                    const uint32_t v = r != 0 ? __funnelshift_r(w[k], w[k + 1], 8 * (4 - r)) : w[k + 1];
+                    if (fits && j < n_words) {
+                        if (s0 >= 0 && s0 + 4 <= cu) {
+                            dst32[j] = v;
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < 4; ++b)
+                                if (s0 + b >= 0 && s0 + b < cu)
+                                    reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
+                        }
                     }
-                }
-                if (HIST) {
-                    // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
-                    uint32_t w = hi;
+                    if (HIST) {
+                        // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
+                        uint32_t x = w[k + 1];
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        if (4 * j + b < cu) atomicAdd(my_hist + (w & 0xFFu), 1);
-                        w >>= 8;
+                        for (int b = 0; b < 4; ++b) {
+                            if (4 * j + b < cu) atomicAdd(my_hist + (x & 0xFFu), 1);
+                            x >>= 8;
+                        }
                     }
                 }
             }
