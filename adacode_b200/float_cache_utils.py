@@ -860,6 +860,7 @@ class Float11Cache(Cache):
             layer.hist_reduce = hist_reduce
         self._init_adjust_schedule(need_adjust, update_steps, block_size, layout)
         self.peak_mem = 0
+        self._fused_decode = False         # set by hf_attention.fused_decode
         self.layout = layout
         self.seq_tile_size = seq_tile_size if seq_tile_size is not None else block_size
         self.auto_init_compress_params = auto_init_compress_params
@@ -906,9 +907,15 @@ class Float11Cache(Cache):
             elif layer.has_pending_dense_block() and not layer.has_pending_adjust_work():
                 layer.apply_pending_dense_block_if_needed()
         need_adjust = self.need_adjust and self.steps % self.update_steps == 0
+        fused = getattr(self, '_fused_decode', False) and key_states.shape[-2] == 1 and layer.is_initialized
+        if fused:
+            # hf_attention.fused_decode: the step's attention reads the packed planes itself
+            cache_kwargs = dict(cache_kwargs or {}, float11_skip_materialize=True)
         result = layer.update(key_states, value_states, need_adjust, cache_kwargs)
         if layer_idx == len(self.layers) - 1:
             self.steps += 1
+        if fused:
+            return key_states, value_states
         return result['key_states'], result['value_states']
 
     def decode_attention(self, query: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,

@@ -155,3 +155,50 @@ def test_rejects_unsupported_shapes(cuda_device):
         attention.decode_attention(q96, [], [], k96, k96)          # head_dim outside {64, 128}
     with pytest.raises(ValueError):
         attention.decode_attention(q16[:, :1], [], [])             # empty cache
+
+
+def test_hf_decode_steps_with_fused_attention(cuda_device):
+    """A small random-init Llama (head_dim 128, grouped queries) decodes through the fused kernel
+    (``hf_attention``): fed the same tokens, the cache follows the same packing schedule as with the
+    materialising path, no dense K/V is rebuilt after the prefill, and every step's logits stay
+    within 10 % of the logits' spread of the ``DynamicCache`` run (a few bf16 steps of the logits:
+    the network runs in bf16 and two attention kernels round differently).  (Free-running greedy tokens are
+    not compared: a random-init model's logits are nearly tied, and the fused kernel sums in a
+    different order than SDPA, so one flipped arg-max would fork the sequences.)"""
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+    from adacode_b200 import Float11Cache, hf_attention
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, vocab_size=1000, max_position_embeddings=1024)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).to(cuda_device).eval()
+    ids = torch.randint(0, 1000, (2, 340), device=cuda_device)
+    prefill, steps = 200, 140
+    ckw = dict(right=129, exp_bits=4, need_adjust=True, update_steps=128, block_size=128, layout='segmented_tiled')
+
+    def run(cache):
+        with torch.no_grad():
+            logits = [model(ids[:, :prefill], past_key_values=cache, use_cache=True).logits[:, -1].float()]
+            for t in range(prefill, prefill + steps):
+                logits.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits[:, -1].float())
+        return torch.stack(logits)
+
+    ref = run(DynamicCache(config=cfg))
+    plain = Float11Cache(cfg, **ckw)
+    got_plain = run(plain)
+    assert torch.equal(ref, got_plain)                       # lossless cache, same attention kernel
+    model.config._attn_implementation = hf_attention.register()
+    fused = Float11Cache(cfg, **ckw)
+    with hf_attention.fused_decode(fused):
+        got_fused = run(fused)
+    spread = ref.std().item()
+    worst = (got_fused - ref).abs().max().item()
+    assert worst <= 0.1 * spread, f'max logit difference {worst:.4f} against a spread of {spread:.4f}'
+    assert (got_fused.argmax(-1) == ref.argmax(-1)).float().mean().item() >= 0.9
+    # same packing schedule (the cached values themselves differ in the last bits from layer 1 on,
+    # because they are computed from the previous layer's attention output)
+    mp, mf = plain.get_memory(), fused.get_memory()
+    for key in ('compressed_block_flushes', 'stored_residual_seq_len', 'stored_compressed_prefix_seq_len'):
+        assert mp[key] == mf[key]
+    assert abs(mp['kv_compressed_memory'] - mf['kv_compressed_memory']) <= 0.01 * mp['kv_compressed_memory']
+    assert mf['materialize_calls'] == 0 and mp['materialize_calls'] > 0
+    assert plain.layers[0].segment_params() == fused.layers[0].segment_params()      # layer 0 sees identical K/V
