@@ -207,3 +207,22 @@ def test_pack_pair_equals_two_packs(cuda_device):
                 assert torch.equal(a, b)
             assert np.array_equal(hist_host, ref_hist.cpu().numpy())
     codec.check_device_status(cuda_device)
+
+
+def test_copy_to_host_refuses_memory_the_device_cannot_address(cuda_device):
+    """``adacode_copy_to_host`` only launches towards page-locked host memory: pageable host memory
+    and device memory are refused with ADACODE_ERR_INVALID_ARG before any kernel runs."""
+    import ctypes
+    from adacode_b200 import _lib
+    L = _lib.lib()
+    src = torch.arange(16, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    pageable = (ctypes.c_uint32 * 16)()
+    assert L.adacode_copy_to_host(src.data_ptr(), ctypes.addressof(pageable), 64, stream) == _lib.ERR_INVALID_ARG
+    other = torch.empty(16, dtype=torch.int32, device=cuda_device)
+    assert L.adacode_copy_to_host(src.data_ptr(), other.data_ptr(), 64, stream) == _lib.ERR_INVALID_ARG
+    pinned = torch.zeros(16, dtype=torch.int32).pin_memory()
+    assert L.adacode_copy_to_host(src.data_ptr(), pinned.data_ptr(), 62, stream) == _lib.ERR_INVALID_ARG   # not a multiple of 4
+    assert L.adacode_copy_to_host(src.data_ptr(), pinned.data_ptr(), 64, stream) == _lib.OK
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(pinned, src.cpu())
