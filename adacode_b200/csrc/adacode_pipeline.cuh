@@ -599,7 +599,12 @@ struct PackPipeArgs {
 };
 
 // Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets.
-// Run by the 256 consumer threads of the CTA that finished last.
+// Run by the consumer threads of the CTA that finished last, while the rest of the GPU is idle,
+// so it is kept short: every thread takes a run of kScanRun consecutive tiles, fetches their
+// counts with independent loads (one memory round trip per pass of 512 x kScanRun tiles), and
+// one block scan of the run totals gives every tile its prefix.
+constexpr int kScanRun = 8;
+
 __device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s_carry, int *s_scan) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -607,9 +612,16 @@ __device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s
         a.seg_off[0] = 0;
     }
     consumer_sync();
-    for (int64_t base = 0; base < a.n_tiles; base += kConsumerThreads) {
-        const int64_t t = base + tid;
-        int x = (t < a.n_tiles) ? __ldcg(a.tile_counts + t) : 0;
+    const int64_t per_pass = (int64_t)kConsumerThreads * kScanRun;
+    for (int64_t pass = 0; pass < a.n_tiles; pass += per_pass) {
+        const int64_t t0 = pass + (int64_t)tid * kScanRun;
+        int c[kScanRun];
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < a.n_tiles) ? __ldcg(a.tile_counts + t0 + i) : 0;
+        int run = 0;
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) run += c[i];
+        int x = run;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int u = __shfl_up_sync(kFull, x, d);
@@ -624,19 +636,25 @@ __device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s
             wp += (i < warp) ? v : 0;
             tot += v;
         }
-        const long long incl = *s_carry + wp + x;
-        if (t < a.n_tiles) {
-            a.tile_base[t] = (int32_t)incl;
-            if ((t + 1) % a.BH == 0) a.seg_off[(t + 1) / a.BH] = incl;
+        long long incl = *s_carry + wp + (x - run);       // escapes before this thread's run
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) {
+            const int64_t t = t0 + i;
+            incl += c[i];
+            c[i] = (int)incl;                             // inclusive prefix over the whole call
+            if (t < a.n_tiles && (t + 1) % a.BH == 0) a.seg_off[(t + 1) / a.BH] = incl;
+        }
+        consumer_sync();                                  // segment offsets of this pass are written
+        if (tid == 0) *s_carry += tot;
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) {
+            const int64_t t = t0 + i;
+            if (t < a.n_tiles) {
+                const int64_t blk = t / a.BH;
+                a.tile_base[t] = c[i] - (blk > 0 ? (int)a.seg_off[blk] : 0);
+            }
         }
         consumer_sync();
-        if (tid == 0) *s_carry += tot;
-        consumer_sync();
-    }
-    __threadfence_block();
-    for (int64_t t = tid; t < a.n_tiles; t += kConsumerThreads) {
-        const int64_t blk = t / a.BH;
-        if (blk > 0) a.tile_base[t] -= (int32_t)a.seg_off[blk];
     }
     if (tid == 0) *a.done = 0u;
 }
