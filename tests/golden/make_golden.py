@@ -47,7 +47,9 @@ def _import_reference(path: str):
 
 
 def main() -> None:
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    if len(sys.argv) < 2:
+        raise SystemExit('usage: make_golden.py <path of the reference kv_compression package checkout>')
+    ref_path = sys.argv[1]
     _import_reference(ref_path)
     import numpy as np
     import torch
@@ -93,7 +95,7 @@ def main() -> None:
             p = O.pack_block(x, right, nbits, need_hist=True)
             assert scenarios._sha(p.invalid_exp) == d['invalid_exp'] and scenarios._sha(p.exp_data) == d['exp_data']
             assert np.array_equal(O.unpack_block(p), O.as_u16(x))
-    # known answers: the survey's probe and the reference's validation fixture
+    # known answers: a seeded probe tensor and the reference's validation fixture
     torch.manual_seed(0)
     x = (torch.randn(1, 8, 128, 128) * 0.7).to(torch.bfloat16)
     x.view(-1)[5] = 0.0
