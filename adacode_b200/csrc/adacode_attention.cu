@@ -375,7 +375,6 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
 template <int N>
 __device__ __forceinline__ void decode_unit_swz(AttnPipeSmem &s, const UnpackStage &st, uint64_t *empty_bar,
                                                 const uint32_t *lut, int32_t *status) {
-    constexpr int CB = 2 * N;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const UnitMeta m = st.meta;
     const int chunks = m.elems >> 4;
@@ -383,31 +382,7 @@ __device__ __forceinline__ void decode_unit_swz(AttnPipeSmem &s, const UnpackSta
     uint4 o[kPCPT][2];
     uint32_t zm[kPCPT][2];
     int zc[kPCPT];
-#pragma unroll
-    for (int k = 0; k < kPCPT; ++k) {
-        const int c = warp * (kPCPT * 32) + k * 32 + lane;
-        uint32_t g[2] = {0u, 0u};
-        uint4 sv = make_uint4(0, 0, 0, 0);
-        const bool valid = c < chunks;
-        if (valid) {
-            sv = *reinterpret_cast<const uint4 *>(st.sm + c * 16);
-            load_chunk_codes<N, 16>(st.codes + c * CB, g);
-        }
-        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-        zc[k] = 0;
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            zm[k][q] = valid ? zero_slots<N>(g[q]) : 0u;
-            zc[k] += __popc(zm[k][q]);
-            uint32_t ew[4];
-            decode_group<N>(lut, g[q], ew);
-            const uint32_t s0 = sw[2 * q], s1 = sw[2 * q + 1];
-            o[k][q].x = ew[0] | (__byte_perm(s0, 0u, 0x1100) & 0x807F807Fu);
-            o[k][q].y = ew[1] | (__byte_perm(s0, 0u, 0x3322) & 0x807F807Fu);
-            o[k][q].z = ew[2] | (__byte_perm(s1, 0u, 0x1100) & 0x807F807Fu);
-            o[k][q].w = ew[3] | (__byte_perm(s1, 0u, 0x3322) & 0x807F807Fu);
-        }
-    }
+    decode_chunks<N>(st, lut, chunks, o, zm, zc);
     int incl[kPCPT];
     const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;

@@ -320,19 +320,15 @@ __device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, 
     }
 }
 
+// Register phase of a unit, shared by the unpack kernel and the fused attention kernel: every
+// consumer thread decodes its kPCPT chunks of the staged planes into registers (exponent fields
+// from the table, 0 where the code is 0; sign and mantissa merged in) and notes where the
+// escapes are (zm: one bit per code-0 slot of each group word; zc: their number per chunk).
 template <int N>
-__device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
-                                            int &consumed, bool rows_contig, int D, long long ds,
-                                            int32_t *status) {
+__device__ __forceinline__ void decode_chunks(const UnpackStage &st, const uint32_t *lut, int chunks,
+                                              uint4 (&o)[kPCPT][2], uint32_t (&zm)[kPCPT][2], int (&zc)[kPCPT]) {
     constexpr int CB = 2 * N;   // code bytes per 16-element chunk
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const UnitMeta m = st.meta;
-    if (m.first_unit_of_tile) consumed = 0;
-    const int chunks = m.elems >> 4;
-
-    uint4 o[kPCPT][2];
-    uint32_t zm[kPCPT][2];
-    int zc[kPCPT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = warp * (kPCPT * 32) + k * 32 + lane;
@@ -350,7 +346,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
             zm[k][q] = valid ? zero_slots<N>(g[q]) : 0u;
             zc[k] += __popc(zm[k][q]);
             uint32_t ew[4];
-            decode_group<N>(s.lut, g[q], ew);
+            decode_group<N>(lut, g[q], ew);
             const uint32_t s0 = sw[2 * q], s1 = sw[2 * q + 1];
             // sign and mantissa: each byte doubled into its 16-bit lane, then masked into place
             o[k][q].x = ew[0] | (__byte_perm(s0, 0u, 0x1100) & 0x807F807Fu);
@@ -359,6 +355,21 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
             o[k][q].w = ew[3] | (__byte_perm(s1, 0u, 0x3322) & 0x807F807Fu);
         }
     }
+}
+
+template <int N>
+__device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
+                                            int &consumed, bool rows_contig, int D, long long ds,
+                                            int32_t *status) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const UnitMeta m = st.meta;
+    if (m.first_unit_of_tile) consumed = 0;
+    const int chunks = m.elems >> 4;
+
+    uint4 o[kPCPT][2];
+    uint32_t zm[kPCPT][2];
+    int zc[kPCPT];
+    decode_chunks<N>(st, s.lut, chunks, o, zm, zc);
     int incl[kPCPT];
     const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;
