@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_decode_attn(const AttnArgs a) 
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttnSmem &s = *reinterpret_cast<AttnSmem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int split = blockIdx.x, bh = blockIdx.y;
+    const int bh = blockIdx.x, split = blockIdx.y;      // (batch, KV head) on x: no 65 535 limit
     const int b = bh / a.Hkv, hkv = bh - b * a.Hkv;
     const int G = a.G, D = a.D;
 
@@ -563,7 +563,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
     AttnPipeSmem &s = *reinterpret_cast<AttnPipeSmem *>(smem_raw);
     const AttnArgs &a = pa.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int split = blockIdx.x, bh = blockIdx.y;
+    const int bh = blockIdx.x, split = blockIdx.y;      // (batch, KV head) on x: no 65 535 limit
     const int b = bh / a.Hkv, hkv = bh - b * a.Hkv;
     const int G = a.G;
 
@@ -776,9 +776,9 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         u.dst = nullptr, u.db = 0, u.dh = 0, u.ds = 0, u.status = status;
         pa.k = u, pa.v = u;
         pa.k.seg = k_segments_dev, pa.v.seg = v_segments_dev;
-        k_decode_attn_pipe<<<dim3(n_splits, B * Hkv), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
+        k_decode_attn_pipe<<<dim3(B * Hkv, n_splits), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
     } else {
-        k_decode_attn<<<dim3(n_splits, B * Hkv), kAttnThreads, sizeof(AttnSmem), st>>>(a);
+        k_decode_attn<<<dim3(B * Hkv, n_splits), kAttnThreads, sizeof(AttnSmem), st>>>(a);
     }
     if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;
     k_decode_attn_combine<<<B * Hq, D, 0, st>>>(a.part_o, a.part_ml, Hq, Hkv, G, D, n_splits, (uint16_t *)out_bf16);
