@@ -7,6 +7,7 @@ Public surface (same names as the reference package ``kv_compression``):
   ``compress_tiled_tensor``, ``materialize_tiled_state``, ``TiledCompressedTensor``   codec
   ``export_initial_compress_parameters``          best_bit_analysis_kv_cache
   ``model_config_map``                            model_configs
+  ``extract_exp_freq``, ``merge_exp_freq``        export_kvcache_status (exponent statistics only)
 and, without a reference counterpart, ``decode_attention`` (attention) — one decode step of
 attention computed from the packed planes.
 """

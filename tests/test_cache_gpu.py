@@ -7,10 +7,11 @@ import os
 import pickle
 import warnings
 
+import numpy as np
 import pytest
 import torch
 
-from tests import scenarios
+from tests import scenarios, synth
 from tests.test_state_machine_cpu import GOLDEN, assert_digest_equal, make_cache_factory
 
 pytestmark = pytest.mark.gpu
@@ -161,3 +162,46 @@ def test_mla_true_dimensions(cuda_device):
         assert np.array_equal(seg.invalid_exp.cpu().numpy(), ref.invalid_exp)
         mem = cache.get_memory()
         assert mem['mla_compress_rope'] == compress_rope and mem['kv_compressed_memory'] < mem['kv_original_memory']
+
+
+def test_calibration_producer_feeds_the_consumer(cuda_device, tmp_path):
+    """``extract_exp_freq`` over a live ``DynamicCache`` gives the oracle's exponent histograms
+    (prefill / decode split), two batches merge bin by bin, and the JSON it is written to yields
+    the windows the calibration rule picks on those histograms."""
+    import json
+    from transformers import DynamicCache
+    from adacode_b200 import export_initial_compress_parameters
+    from adacode_b200.export_kvcache_status import extract_exp_freq, merge_exp_freq
+    from oracle import float11_oracle as O
+    layers, prefill = 3, 200
+    results, tensors = [], []
+    for batch in range(2):
+        cache = DynamicCache()
+        per_layer = []
+        for l in range(layers):
+            k = synth.kv_tensor((2, 4, 260, 64), seed=100 + 10 * batch + l, key_offset=True)
+            v = synth.kv_tensor((2, 4, 260, 64), seed=200 + 10 * batch + l)
+            cache.update(k.to(cuda_device), v.to(cuda_device), l)
+            per_layer.append((k, v))
+        tensors.append(per_layer)
+        results.append(extract_exp_freq(cache, 'exp', prefill_len=prefill))
+    for batch in range(2):
+        for l in range(layers):
+            k, v = tensors[batch][l]
+            got = results[batch][l]
+            assert got['prefill_keys'] == O.exponent_hist(k[:, :, :prefill].contiguous()).tolist()
+            assert got['decode_keys'] == O.exponent_hist(k[:, :, prefill:].contiguous()).tolist()
+            assert got['prefill_values'] == O.exponent_hist(v[:, :, :prefill].contiguous()).tolist()
+            assert got['decode_values'] == O.exponent_hist(v[:, :, prefill:].contiguous()).tolist()
+    merged = merge_exp_freq(results[0], results[1])
+    assert merged[1]['decode_keys'] == [a + b for a, b in zip(results[0][1]['decode_keys'], results[1][1]['decode_keys'])]
+    path = tmp_path / 'stats.json'
+    path.write_text(json.dumps({'c4': {str(l): merged[l] for l in range(layers)}}))
+    rights, nbits = export_initial_compress_parameters(str(path), 'c4', 'merge')
+    for l in range(layers):
+        kh = np.asarray(merged[l]['prefill_keys']) + np.asarray(merged[l]['decode_keys'])
+        vh = np.asarray(merged[l]['prefill_values']) + np.asarray(merged[l]['decode_values'])
+        assert (rights[l][0], nbits[l][0]) == tuple(O.calibrate_coo(kh))
+        assert (rights[l][1], nbits[l][1]) == tuple(O.calibrate_coo(vh))
+    whole = extract_exp_freq(cache)                      # no split
+    assert whole[0]['keys'] == O.exponent_hist(tensors[1][0][0]).tolist()
