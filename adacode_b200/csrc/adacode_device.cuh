@@ -44,6 +44,27 @@ __device__ __forceinline__ uint32_t zero_slots(uint32_t g) {
     return ~m & SlotLsb<N>::v;
 }
 
+// The eight slot bits of zero_slots<N>() (one per N-bit slot, at the slot's least significant bit)
+// moved next to each other: slot j -> bit j, so element k of the group sits at bit 7 - k.
+template <int N>
+__device__ __forceinline__ uint32_t compress_slots(uint32_t z) {
+    if constexpr (N == 1) {
+        return z;
+    } else if constexpr (N == 2) {
+        z = (z | (z >> 1)) & 0x3333u;
+        z = (z | (z >> 2)) & 0x0F0Fu;
+        return (z | (z >> 4)) & 0xFFu;
+    } else if constexpr (N == 3) {
+        z = (z | (z >> 2)) & 0x0C30C3u;
+        z = (z | (z >> 4)) & 0x00F00Fu;
+        return (z | (z >> 8)) & 0xFFu;
+    } else {
+        z = (z | (z >> 3)) & 0x03030303u;
+        z = (z | (z >> 6)) & 0x000F000Fu;
+        return (z | (z >> 12)) & 0xFFu;
+    }
+}
+
 // Eight exponent codes of eight consecutive bf16 (four words) as one group word:
 // element k sits at bits [(7-k)*N, (8-k)*N).  Out-of-window exponents code as 0.
 template <int N>

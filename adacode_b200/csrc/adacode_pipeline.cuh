@@ -377,47 +377,61 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     consumer_sync();
     int wprefix, unit_tot;
     cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+    static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
+    const int c0 = warp * (kPCPT * 32) + lane;
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
-        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        const int c = c0 + k * 32;
         if (c < chunks) {
             uint16_t *ow = s.out + c * 16;
             reinterpret_cast<uint4 *>(ow)[0] = o[k][0];
             reinterpret_cast<uint4 *>(ow)[1] = o[k][1];
-            if (zc[k] != 0) {
-                int r = consumed + wprefix + incl[k] - zc[k];     // rank inside the tile
-                if (r + zc[k] <= m.esc_staged) {
-                    // the exponent field in s.out is zero at escaped positions (code 0 decodes to 0),
-                    // so the escape byte is OR-ed in with a shared-memory reduction: no
-                    // read-modify-write round trip in this thread
-                    const uint8_t *ep = st.esc + m.esc_shift + r;
-                    uint32_t *ow32 = reinterpret_cast<uint32_t *>(ow);
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        uint32_t z = zm[k][q];
-                        while (z) {
-                            const int pos = 31 - __clz(z);
-                            z ^= 1u << pos;
-                            const int el = q * 8 + 7 - pos / N;
-                            atomicOr(ow32 + (el >> 1), (uint32_t)(*ep++) << (7 + 16 * (el & 1)));
-                        }
-                    }
-                } else {
-                    // beyond the staged window (or beyond the stream): fetch from global memory
+        }
+    }
+    if (zc[0] + zc[1] != 0) {
+        // ranks inside the tile of the first escape of either chunk
+        const int r0 = consumed + wprefix + incl[0] - zc[0], r1 = consumed + wprefix + incl[1] - zc[1];
+        const bool staged = (zc[0] == 0 || r0 + zc[0] <= m.esc_staged) && (zc[1] == 0 || r1 + zc[1] <= m.esc_staged);
+        if (staged) {
+            // One loop over the escapes of both chunks (four groups): a warp iterates as often as its
+            // busiest lane has escapes, and per-lane totals over 32 elements vary much less than
+            // per-group counts over 8, so this takes about half the iterations of four separate loops.
+            // mask: chunk 0 elements 0..15, then chunk 1 elements 0..15, from the most significant bit.
+            uint32_t todo = (compress_slots<N>(zm[0][0]) << 24) | (compress_slots<N>(zm[0][1]) << 16) |
+                            (compress_slots<N>(zm[1][0]) << 8) | compress_slots<N>(zm[1][1]);
+            // The exponent field in s.out is zero at escaped positions (code 0 decodes to 0), so the
+            // escape byte is OR-ed in with a shared-memory reduction: no read-modify-write round trip.
+            const uint8_t *ep = st.esc + m.esc_shift + r0;
+            const int skip = r1 - r0 - zc[0];             // from chunk 0's escapes to chunk 1's
+            uint32_t *ow32 = reinterpret_cast<uint32_t *>(s.out + c0 * 16);
+            int n = 0;
+            while (todo) {
+                const int i = __clz(todo);
+                todo &= ~(0x80000000u >> i);
+                const uint32_t e = ep[n + (i >> 4) * skip];
+                ++n;
+                // chunk 1 lies 32 chunks = 256 words further on; (i >> 1) & 7 is the word inside the chunk
+                atomicOr(ow32 + (((i >> 4) << 8) | ((i >> 1) & 7)), e << (7 + 16 * (i & 1)));
+            }
+        } else {
+            // beyond the staged window (or beyond the stream): fetch from global memory
 #pragma unroll 1
-                    for (int q = 0; q < 2; ++q) {
-                        uint32_t z = zm[k][q];
-                        while (z) {
-                            const int pos = 31 - __clz(z);
-                            z ^= 1u << pos;
-                            uint32_t e = 0;
-                            if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
-                            else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
-                            else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
-                            ++r;
-                            uint16_t *pw = ow + (q * 8 + 7 - pos / N);
-                            *pw = (uint16_t)((*pw & 0x807Fu) | (e << 7));
-                        }
+            for (int k = 0; k < kPCPT; ++k) {
+                uint16_t *ow = s.out + (c0 + k * 32) * 16;
+                int r = k == 0 ? r0 : r1;
+#pragma unroll 1
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t z = zm[k][q];
+                    while (z) {
+                        const int pos = 31 - __clz(z);
+                        z ^= 1u << pos;
+                        uint32_t e = 0;
+                        if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
+                        else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
+                        else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
+                        ++r;
+                        uint16_t *pw = ow + (q * 8 + 7 - pos / N);
+                        *pw = (uint16_t)((*pw & 0x807Fu) | (e << 7));
                     }
                 }
             }
@@ -725,27 +739,33 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
     consumer_sync();
     int wprefix, unit_tot;
     cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+    static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
+    const int c0 = warp * (kPCPT * 32) + lane;
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
-        const int c = warp * (kPCPT * 32) + k * 32 + lane;
+        const int c = c0 + k * 32;
         if (c < chunks) {
             *reinterpret_cast<uint4 *>(s.sm + c * 16) = smv[k];
             const uint32_t gg[2] = {g[2 * k], g[2 * k + 1]};
             store_chunk_codes<N, 16>(s.codes + c * CB, gg);
-            if (zc[k] != 0) {
-                uint8_t *out = s.esc + wprefix + incl[k] - zc[k];
-                const uint16_t *src = st.in + c * 16;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint32_t z = zm[k][q];
-                    while (z) {
-                        const int pos = 31 - __clz(z);
-                        z ^= 1u << pos;
-                        const uint32_t e = (src[q * 8 + 7 - pos / N] >> 7) & 0xFFu;
-                        *out++ = (uint8_t)e;
-                    }
-                }
-            }
+        }
+    }
+    if (zc[0] + zc[1] != 0) {
+        // One loop over the escapes of both chunks (see unpack_unit): chunk 0 elements 0..15, then
+        // chunk 1 elements 0..15, from the most significant bit of the mask.
+        uint32_t todo = (compress_slots<N>(zm[0][0]) << 24) | (compress_slots<N>(zm[0][1]) << 16) |
+                        (compress_slots<N>(zm[1][0]) << 8) | compress_slots<N>(zm[1][1]);
+        uint8_t *out = s.esc + wprefix + incl[0] - zc[0];
+        const int skip = incl[1] - zc[1] - incl[0];        // from chunk 0's escape bytes to chunk 1's
+        const uint16_t *src = st.in + c0 * 16;
+        int n = 0;
+        while (todo) {
+            const int i = __clz(todo);
+            todo &= ~(0x80000000u >> i);
+            // chunk 1 lies 32 chunks = 512 elements further on
+            const uint32_t e = (src[((i >> 4) << 9) | (i & 15)] >> 7) & 0xFFu;
+            out[n + (i >> 4) * skip] = (uint8_t)e;
+            ++n;
         }
     }
     mbar_arrive(empty_bar);
