@@ -176,12 +176,14 @@ __global__ void __launch_bounds__(kAttnThreads) k_decode_attn(const AttnArgs a) 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int bh = blockIdx.x, split = blockIdx.y;      // (batch, KV head) on x: no 65 535 limit
     const int b = bh / a.Hkv, hkv = bh - b * a.Hkv;
-    const int G = a.G, D = a.D;
+    // query heads of the group are handled eight at a time: blockIdx.z picks the eight
+    const int Gt = a.G, gz = blockIdx.z * kMaxGroup;
+    const int G = Gt - gz < kMaxGroup ? Gt - gz : kMaxGroup, D = a.D;
 
     // queries of this KV head's group, as fp32, pre-multiplied by the softmax scale
     for (int i = tid; i < G * D; i += kAttnThreads) {
         const int g = i / D, d = i - g * D;
-        const uint16_t raw = a.q[(long long)b * a.q_sb + (long long)(hkv * G + g) * a.q_sh + d];
+        const uint16_t raw = a.q[(long long)b * a.q_sb + (long long)(hkv * Gt + gz + g) * a.q_sh + d];
         s.q[g][d] = __uint_as_float((uint32_t)raw << 16) * a.scale;
     }
     for (int i = tid; i < kTileTokens * kMaxGroup; i += kAttnThreads) (&s.p[0][0])[i] = 0.f;
@@ -278,10 +280,10 @@ __global__ void __launch_bounds__(kAttnThreads) k_decode_attn(const AttnArgs a) 
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g) {
         if (g < G) {
-            if (tid < D) a.part_o[(slot * G + g) * D + tid] = o[g];
+            if (tid < D) a.part_o[(slot * Gt + gz + g) * D + tid] = o[g];
             if (tid == g) {
-                a.part_ml[(slot * G + g) * 2 + 0] = m[g];
-                a.part_ml[(slot * G + g) * 2 + 1] = l[g];
+                a.part_ml[(slot * Gt + gz + g) * 2 + 0] = m[g];
+                a.part_ml[(slot * Gt + gz + g) * 2 + 1] = l[g];
             }
         }
     }
@@ -565,7 +567,8 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int bh = blockIdx.x, split = blockIdx.y;      // (batch, KV head) on x: no 65 535 limit
     const int b = bh / a.Hkv, hkv = bh - b * a.Hkv;
-    const int G = a.G;
+    const int Gt = a.G, gz = blockIdx.z * kMaxGroup;     // eight query heads of the group per CTA
+    const int G = Gt - gz < kMaxGroup ? Gt - gz : kMaxGroup;
 
     if (tid == 0) {
 #pragma unroll
@@ -579,7 +582,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
     for (int i = tid; i < kMaxGroup * kQPad; i += kPipeThreads) {
         const int g = i / kQPad, d = i - g * kQPad;
         uint16_t v = 0;
-        if (g < G && d < kAD) v = a.q[(long long)b * a.q_sb + (long long)(hkv * G + g) * a.q_sh + d];
+        if (g < G && d < kAD) v = a.q[(long long)b * a.q_sb + (long long)(hkv * Gt + gz + g) * a.q_sh + d];
         s.q[g][d] = v;
         s.p[g][d] = 0;
     }
@@ -668,18 +671,18 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
     if (warp < 8) {
         const int g0 = 2 * (lane & 3), d0 = warp * 16 + (lane >> 2);
         if (g0 < G) {
-            a.part_o[(slot * G + g0) * kAD + d0] = oacc[0];
-            a.part_o[(slot * G + g0) * kAD + d0 + 8] = oacc[2];
+            a.part_o[(slot * Gt + gz + g0) * kAD + d0] = oacc[0];
+            a.part_o[(slot * Gt + gz + g0) * kAD + d0 + 8] = oacc[2];
         }
         if (g0 + 1 < G) {
-            a.part_o[(slot * G + g0 + 1) * kAD + d0] = oacc[1];
-            a.part_o[(slot * G + g0 + 1) * kAD + d0 + 8] = oacc[3];
+            a.part_o[(slot * Gt + gz + g0 + 1) * kAD + d0] = oacc[1];
+            a.part_o[(slot * Gt + gz + g0 + 1) * kAD + d0 + 8] = oacc[3];
         }
     }
     if (tid < G) {
         const float m2 = s.m[parity][tid];
-        a.part_ml[(slot * G + tid) * 2 + 0] = m2 == -INFINITY ? -INFINITY : m2 / kLog2e;   // natural-log domain
-        a.part_ml[(slot * G + tid) * 2 + 1] = s.l[tid];
+        a.part_ml[(slot * Gt + gz + tid) * 2 + 0] = m2 == -INFINITY ? -INFINITY : m2 / kLog2e;   // natural-log domain
+        a.part_ml[(slot * Gt + gz + tid) * 2 + 1] = s.l[tid];
     }
 }
 
@@ -728,7 +731,9 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
                         int32_t *status, void *stream) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_segments < 0 || tail_len < 0) return ADACODE_ERR_INVALID_ARG;
     const int G = Hq / Hkv;
-    if (G > kMaxGroup || seq_tile != kTileTokens || (D != 64 && D != 128)) return ADACODE_ERR_INVALID_ARG;
+    if (seq_tile != kTileTokens || (D != 64 && D != 128)) return ADACODE_ERR_INVALID_ARG;
+    const int head_groups = (G + kMaxGroup - 1) / kMaxGroup;      // CTAs along z, eight query heads each
+    if (head_groups > 65535) return ADACODE_ERR_INVALID_ARG;
     if (!q_bf16 || !out_bf16 || !workspace || !status) return ADACODE_ERR_INVALID_ARG;
     if (n_segments > 0 && (!k_segments_dev || !v_segments_dev)) return ADACODE_ERR_INVALID_ARG;
     if (tail_len > 0 && (!k_tail_bf16 || !v_tail_bf16 || ((uintptr_t)k_tail_bf16 & 3) || ((uintptr_t)v_tail_bf16 & 3) ||
@@ -736,7 +741,7 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         return ADACODE_ERR_INVALID_ARG;
     const int items = n_segments + (tail_len + kTileTokens - 1) / kTileTokens;
     if (items == 0) return ADACODE_ERR_INVALID_ARG;
-    if (n_splits <= 0) n_splits = pick_splits(B, Hkv, items, D);
+    if (n_splits <= 0) n_splits = pick_splits(B, Hkv * head_groups, items, D);
     if (n_splits > kMaxSplits) n_splits = kMaxSplits;
     if (workspace_bytes < adacode_decode_attn_workspace_bytes(B, Hq, D, n_splits)) return ADACODE_ERR_WORKSPACE;
     AttnArgs a;
@@ -776,9 +781,9 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         u.dst = nullptr, u.db = 0, u.dh = 0, u.ds = 0, u.status = status;
         pa.k = u, pa.v = u;
         pa.k.seg = k_segments_dev, pa.v.seg = v_segments_dev;
-        k_decode_attn_pipe<<<dim3(B * Hkv, n_splits), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
+        k_decode_attn_pipe<<<dim3(B * Hkv, n_splits, head_groups), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
     } else {
-        k_decode_attn<<<dim3(B * Hkv, n_splits), kAttnThreads, sizeof(AttnSmem), st>>>(a);
+        k_decode_attn<<<dim3(B * Hkv, n_splits, head_groups), kAttnThreads, sizeof(AttnSmem), st>>>(a);
     }
     if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;
     k_decode_attn_combine<<<B * Hq, D, 0, st>>>(a.part_o, a.part_ml, Hq, Hkv, G, D, n_splits, (uint16_t *)out_bf16);

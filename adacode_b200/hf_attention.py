@@ -14,7 +14,7 @@ the dense tensors, as before.
         out = model.generate(ids, past_key_values=cache, ...)
 
 Limits: every cached token is attended to (no padding mask, no sliding window), head_dim 64 or
-128, at most 8 query heads per KV head.  Results are close to, not bit-identical with, the
+128.  Results are close to, not bit-identical with, the
 materialising path (different summation order), so generated tokens can differ where two
 logits are nearly tied.
 """

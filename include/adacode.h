@@ -225,14 +225,15 @@ size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);
  * stride along D).  Every cached token is visible to the query (no mask).  The planes are
  * decoded tile by tile in shared memory, so HBM sees the packed bytes only; the work is
  * split along the sequence into n_splits parts (<= 0: chosen by the library; at most 128)
- * whose partial results a second kernel merges.
+ * whose partial results a second kernel merges.  A CTA serves up to eight query heads of a group;
+ * larger groups (G > 8) are served by ceil(G / 8) CTAs that each decode the tiles again.
  * The reference implementation has no counterpart: its caches report
  *   decode_impl 'materialize_dense' (float_cache_utils.py:1342) and always rebuild dense K/V
  *   (float11Layer.update, :1278-1316) before the model's own attention runs; the module its
  *   validation script imports for a fused path (ops/kv_attention.py) is not in its tree.
  * Arithmetic: products and sums in fp32 (head_dim 128: bf16 x bf16 tensor-core products with
  * fp32 accumulation, probabilities rounded to bf16 for the weighted sum and its denominator
- * alike; head_dim 64: fp32 throughout), output rounded to bf16 (nearest even).  Requirements: seq_tile == 128, D in {64, 128}, G <= 8, q with unit stride
+ * alike; head_dim 64: fp32 throughout), output rounded to bf16 (nearest even).  Requirements: seq_tile == 128, D in {64, 128}, q with unit stride
  * along D and element strides q_stride_b/h, out contiguous [B][Hq][D].
  */
 int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride_h,

@@ -59,6 +59,8 @@ def _pack_mixed(x, params):
     (3, 4, 4, 64, 4, 1),         # head_dim 64, one dense token
     (1, 8, 2, 64, 0, 200),       # nothing packed yet
     (2, 8, 1, 128, 9, 300),      # multi-query attention, tail longer than two tiles
+    (1, 24, 2, 128, 3, 40),      # twelve query heads per KV head: two CTAs along z (8 + 4)
+    (1, 16, 1, 64, 2, 10),       # sixteen per KV head, head_dim 64
 ])
 @pytest.mark.parametrize('n_splits', [0, 1, 7])
 def test_matches_fp32_attention(cuda_device, B, Hq, Hkv, D, n_seg, tail, n_splits):
@@ -145,16 +147,16 @@ def test_cache_decode_attention_follows_update_schedule(cuda_device):
 
 def test_rejects_unsupported_shapes(cuda_device):
     from adacode_b200 import attention
-    k = synth.kv_tensor((1, 1, 128, 128), seed=1).to(cuda_device)
-    q16 = torch.zeros(1, 16, 128, dtype=torch.bfloat16, device=cuda_device)
-    with pytest.raises(ValueError):
-        attention.decode_attention(q16, [], [], k, k)              # sixteen query heads per KV head
     k96 = synth.kv_tensor((1, 1, 128, 96), seed=1).to(cuda_device)
     q96 = torch.zeros(1, 1, 96, dtype=torch.bfloat16, device=cuda_device)
     with pytest.raises(ValueError):
         attention.decode_attention(q96, [], [], k96, k96)          # head_dim outside {64, 128}
+    q = torch.zeros(1, 6, 128, dtype=torch.bfloat16, device=cuda_device)
+    k = synth.kv_tensor((1, 4, 128, 128), seed=1).to(cuda_device)
     with pytest.raises(ValueError):
-        attention.decode_attention(q16[:, :1], [], [])             # empty cache
+        attention.decode_attention(q, [], [], k, k)                # 6 query heads on 4 KV heads
+    with pytest.raises(ValueError):
+        attention.decode_attention(q[:, :1], [], [])               # empty cache
 
 
 def test_hf_decode_steps_with_fused_attention(cuda_device):
