@@ -319,7 +319,7 @@ __global__ void k_decode_attn_combine(const float *__restrict__ part_o, const fl
 // Pipelined variant for head_dim 128: the unpack pipeline (producer warp, bulk copies into a
 // two-stage ring, 16 consumer warps decoding out of shared memory) feeding tensor-core products.
 // A decoded tile lives in shared memory as 128 rows (tokens) of 256 bytes whose 16-byte pieces are
-// XOR-swizzled with the row index, so that ldmatrix reads it without bank conflicts both as
+// XOR-swizzled with the row index, so that ldmatrix reads it with few bank conflicts both as
 // K (token-major, for scores) and, transposed, as V (for the weighted sum).
 //   scores  S[t][g]   = sum_d K[t][d] q[g][d]   : mma.m16n8k16, A = K rows, B = q (8 query heads)
 //   output  O^T[d][g] = sum_t V[t][d] P[t][g]   : mma.m16n8k16, A = V^T (ldmatrix.trans), B = P
@@ -346,8 +346,13 @@ struct AttnPipeSmem {
     int warp_tot[kPWarps];
 };
 
+// Byte offset of 16-byte piece `piece` of row `row` in the swizzled tile.  Only the two low bits of
+// the row enter the XOR: ldmatrix then sees two-way conflicts (eight rows, four patterns), which
+// hardly matters at sixteen ldmatrix per warp and tile, and in return rows r and r + 4 share one
+// pattern, so the second chunk of a thread (32 chunks = 4 rows further on) lies exactly 1024 bytes
+// after the first and the second piece of a chunk at its first piece's offset XOR 16.
 __device__ __forceinline__ uint32_t swz(int row, int piece) {
-    return (uint32_t)(row * 256 + ((piece ^ (row & 7)) << 4));
+    return (uint32_t)(row * 256 + ((piece ^ (row & 3)) << 4));
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -391,46 +396,56 @@ __device__ __forceinline__ void decode_unit_swz(AttnPipeSmem &s, const UnpackSta
     consumer_sync();           // also: every warp is done reading the previous tile
     int wprefix, unit_tot;
     cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+    static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
+    const int c0 = warp * (kPCPT * 32) + lane;
+    const uint32_t off0 = swz(c0 >> 3, (c0 & 7) * 2);          // chunk 0, first piece
+    uint32_t *tile32 = reinterpret_cast<uint32_t *>(s.tile);
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
-        const int c = warp * (kPCPT * 32) + k * 32 + lane;
-        if (c < chunks) {
-            const int row = c >> 3, piece = (c & 7) * 2;
-            uint8_t *p0 = s.tile + swz(row, piece), *p1 = s.tile + swz(row, piece + 1);
-            *reinterpret_cast<uint4 *>(p0) = o[k][0];
-            *reinterpret_cast<uint4 *>(p1) = o[k][1];
-            if (zc[k] != 0) {
-                int r = wprefix + incl[k] - zc[k];     // rank inside the tile
-                if (r + zc[k] <= m.esc_staged) {
-                    const uint8_t *ep = st.esc + m.esc_shift + r;
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        uint32_t z = zm[k][q];
-                        uint32_t *w32 = reinterpret_cast<uint32_t *>(q == 0 ? p0 : p1);
-                        while (z) {
-                            const int pos = 31 - __clz(z);
-                            z ^= 1u << pos;
-                            const int el = 7 - pos / N;
-                            atomicOr(w32 + (el >> 1), (uint32_t)(*ep++) << (7 + 16 * (el & 1)));
-                        }
-                    }
-                } else {
-                    // beyond the staged window (or beyond the stream): fetch from global memory
+        if (c0 + k * 32 < chunks) {
+            *reinterpret_cast<uint4 *>(s.tile + off0 + 1024 * k) = o[k][0];
+            *reinterpret_cast<uint4 *>(s.tile + (off0 ^ 16u) + 1024 * k) = o[k][1];
+        }
+    }
+    if (zc[0] + zc[1] != 0) {
+        const int r0 = wprefix + incl[0] - zc[0], r1 = wprefix + incl[1] - zc[1];     // ranks inside the tile
+        const bool staged = (zc[0] == 0 || r0 + zc[0] <= m.esc_staged) && (zc[1] == 0 || r1 + zc[1] <= m.esc_staged);
+        const uint32_t base_w = off0 >> 2;
+        if (staged) {
+            // one loop over the escapes of both chunks, as in the unpack kernel: chunk 0 elements
+            // 0..15, then chunk 1 elements 0..15, from the most significant bit of the mask
+            uint32_t todo = (compress_slots<N>(zm[0][0]) << 24) | (compress_slots<N>(zm[0][1]) << 16) |
+                            (compress_slots<N>(zm[1][0]) << 8) | compress_slots<N>(zm[1][1]);
+            const uint8_t *ep = st.esc + m.esc_shift + r0;
+            const int skip = r1 - r0 - zc[0];
+            int n = 0;
+            while (todo) {
+                const int i = __clz(todo);
+                todo &= ~(0x80000000u >> i);
+                const uint32_t e = ep[n + (i >> 4) * skip];
+                ++n;
+                const uint32_t t = (uint32_t)i >> 1;         // bit 2: second piece; bits 0..1: word in the piece
+                atomicOr(tile32 + ((base_w ^ (t & 4u)) + (((uint32_t)i >> 4) << 8) + (t & 3u)), e << (7 + 16 * (i & 1)));
+            }
+        } else {
+            // beyond the staged window (or beyond the stream): fetch from global memory
 #pragma unroll 1
-                    for (int q = 0; q < 2; ++q) {
-                        uint32_t z = zm[k][q];
-                        uint32_t *w32 = reinterpret_cast<uint32_t *>(q == 0 ? p0 : p1);
-                        while (z) {
-                            const int pos = 31 - __clz(z);
-                            z ^= 1u << pos;
-                            const int el = 7 - pos / N;
-                            uint32_t e = 0;
-                            if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
-                            else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
-                            else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
-                            ++r;
-                            atomicOr(w32 + (el >> 1), e << (7 + 16 * (el & 1)));
-                        }
+            for (int k = 0; k < kPCPT; ++k) {
+                int r = k == 0 ? r0 : r1;
+#pragma unroll 1
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t z = k == 0 ? (q == 0 ? zm[0][0] : zm[0][1]) : (q == 0 ? zm[1][0] : zm[1][1]);
+                    uint32_t *w32 = tile32 + ((base_w ^ ((uint32_t)q << 2)) + ((uint32_t)k << 8));
+                    while (z) {
+                        const int pos = 31 - __clz(z);
+                        z ^= 1u << pos;
+                        const int el = 7 - pos / N;
+                        uint32_t e = 0;
+                        if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
+                        else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
+                        else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
+                        ++r;
+                        atomicOr(w32 + (el >> 1), e << (7 + 16 * (el & 1)));
                     }
                 }
             }
