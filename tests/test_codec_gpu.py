@@ -226,3 +226,41 @@ def test_copy_to_host_refuses_memory_the_device_cannot_address(cuda_device):
     assert L.adacode_copy_to_host(src.data_ptr(), pinned.data_ptr(), 64, stream) == _lib.OK
     torch.cuda.synchronize(cuda_device)
     assert torch.equal(pinned, src.cpu())
+
+
+def test_randomised_shapes_windows_and_escape_rates(cuda_device):
+    """Seeded sweep over shapes, code lengths, windows and escape rates (from none to nearly all):
+    every plane equals the oracle's, both unpack entry points round-trip, also through views of a
+    chunk whose escape lists start at arbitrary byte offsets, and pack_pair with tiny capacities."""
+    from adacode_b200 import codec
+    rng = np.random.default_rng(1234)
+    for case in range(60):
+        B, H = int(rng.integers(1, 4)), int(rng.integers(1, 5))
+        n_blocks = int(rng.integers(1, 5))
+        D = int(rng.choice([16, 32, 64, 128, 256]))
+        nbits = int(rng.integers(1, 5))
+        right = int(rng.integers(118, 136))
+        s = float(rng.choice([0.1, 0.5, 1.0, 2.0]))
+        x_cpu = synth.kv_tensor((B, H, 128 * n_blocks, D), seed=1000 + case, s=s, key_offset=bool(case & 1))
+        if case % 3 == 0:
+            x_cpu = synth.inject_escapes(x_cpu, seed=case, left=right - 2 ** nbits + 1, right=right,
+                                         p_window=float(rng.choice([1e-3, 0.05, 0.3])), p_zero=1e-3)
+        x = x_cpu.to(cuda_device)
+        chunk, hist = codec.pack_blocks(x, right, nbits, 128, need_hist=True)
+        _check_chunk_against_oracle(chunk, hist, x_cpu, right, nbits, 128)
+        out = torch.zeros_like(x)
+        codec.unpack_chunk(chunk, out)
+        assert np.array_equal(_u16(out), _u16(x_cpu)), f'case {case}: uniform unpack'
+        # segments in reverse order into a strided destination: tables with per-segment offsets
+        wide = torch.zeros((B, H, 128 * n_blocks + 64, D), dtype=torch.bfloat16, device=cuda_device)
+        segs = chunk.segments()[::-1]
+        offs = [128 * (n_blocks - 1 - j) for j in range(n_blocks)]
+        codec.unpack_segments(segs, wide[:, :, :128 * n_blocks], seq_offsets=offs)
+        assert np.array_equal(_u16(wide[:, :, :128 * n_blocks]), _u16(x_cpu)), f'case {case}: segment unpack'
+        if case % 5 == 0:
+            kc, vc, _, _, _, _ = codec.pack_pair(x, x, (right, nbits), (right - 1, nbits), 128, capacities=(16, 16))
+            assert torch.equal(kc.escapes, chunk.escapes) and torch.equal(kc.codes, chunk.codes)
+            back = torch.zeros_like(x)
+            codec.unpack_chunk(vc, back)
+            assert np.array_equal(_u16(back), _u16(x_cpu)), f'case {case}: pair unpack'
+    codec.check_device_status(cuda_device)
