@@ -88,6 +88,34 @@ def test_matches_fp32_attention(cuda_device, B, Hq, Hkv, D, n_seg, tail, n_split
     _assert_close(out, _reference(q, k, v, scale))
 
 
+def test_randomised_attention_shapes(cuda_device):
+    """Seeded sweep: batch, KV heads, heads per group (also beyond eight), both head sizes, segment
+    counts, residual lengths, split counts, code lengths and windows per segment."""
+    import numpy as np
+    from adacode_b200 import attention, codec
+    rng = np.random.default_rng(77)
+    for case in range(24):
+        B, Hkv = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        G = int(rng.choice([1, 2, 3, 4, 7, 8, 9, 16]))
+        D = int(rng.choice([64, 128, 128]))
+        n_seg, tail = int(rng.integers(0, 7)), int(rng.integers(0, 260))
+        if n_seg == 0 and tail == 0:
+            tail = 5
+        S = n_seg * 128 + tail
+        k = synth.kv_tensor((B, Hkv, S, D), seed=300 + case, key_offset=True, s=0.5).to(cuda_device)
+        v = synth.kv_tensor((B, Hkv, S, D), seed=400 + case, s=0.7).to(cuda_device)
+        q = (torch.randn(B, Hkv * G, D, generator=torch.Generator('cpu').manual_seed(case)) * 0.5).to(torch.bfloat16).to(cuda_device)
+        params = [(int(rng.integers(124, 133)), int(rng.integers(1, 5))) for _ in range(3)]
+        kseg = _pack_mixed(k[:, :, :n_seg * 128], params)
+        vseg = _pack_mixed(v[:, :, :n_seg * 128], params[::-1])
+        k_tail = k[:, :, n_seg * 128:] if tail else None
+        v_tail = v[:, :, n_seg * 128:] if tail else None
+        scale = float(rng.choice([1.0 / math.sqrt(D), 0.05, 0.3]))
+        out = attention.decode_attention(q, kseg, vseg, k_tail, v_tail, scale=scale, n_splits=int(rng.choice([0, 1, 3, 11])))
+        _assert_close(out, _reference(q, k, v, scale))
+    codec.check_device_status(cuda_device)
+
+
 def test_escape_heavy_planes_and_peaked_softmax(cuda_device):
     """Windows that miss most exponents (every second element escapes) and scores large enough
     that a handful of tokens carry all the probability mass."""
