@@ -20,6 +20,8 @@ ERR_TOO_LARGE = -5
 STATIC_SCRATCH_BYTES = 4 * 1024 * 1024 + 512 * 1024
 STATUS_ESCAPE_OVERFLOW = 1
 STATUS_ESCAPE_UNDERRUN = 2
+STATUS_TIMEOUT = 4
+STATUS_MISALIGNED = 8
 
 # every symbol include/adacode.h declares
 EXPORTED_SYMBOLS = (
@@ -27,6 +29,7 @@ EXPORTED_SYMBOLS = (
     'adacode_pack_tiles', 'adacode_unpack_tiles', 'adacode_unpack_segments', 'adacode_hist_bf16',
     'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host', 'adacode_pack_tiles_static',
     'adacode_decode_attn_workspace_bytes', 'adacode_decode_attn', 'adacode_copy_to_host',
+    'adacode_pack_jobs', 'adacode_unpack_jobs', 'adacode_max_jobs', 'adacode_debug_set_wait_limit',
 )
 
 
@@ -36,6 +39,26 @@ class Segment(ctypes.Structure):
         ('sign_mant', ctypes.c_void_p), ('codes', ctypes.c_void_p), ('escapes', ctypes.c_void_p),
         ('tile_base', ctypes.c_void_p), ('escapes_len', ctypes.c_int64), ('dst_seq_offset', ctypes.c_int64),
         ('left', ctypes.c_int32), ('nbits', ctypes.c_int32),
+    ]
+
+
+class PackJob(ctypes.Structure):
+    """Mirror of ``struct adacode_pack_job``."""
+    _fields_ = [
+        ('src_bf16', ctypes.c_void_p), ('stride_b', ctypes.c_int64), ('stride_h', ctypes.c_int64),
+        ('stride_s', ctypes.c_int64), ('n_blocks', ctypes.c_int32), ('right', ctypes.c_int32),
+        ('sign_mant', ctypes.c_void_p), ('codes', ctypes.c_void_p), ('escapes', ctypes.c_void_p),
+        ('escapes_capacity', ctypes.c_int64), ('tile_base', ctypes.c_void_p),
+        ('seg_escape_offsets', ctypes.c_void_p), ('hist256', ctypes.c_void_p),
+    ]
+
+
+class UnpackJob(ctypes.Structure):
+    """Mirror of ``struct adacode_unpack_job``."""
+    _fields_ = [
+        ('segments_dev', ctypes.c_void_p), ('n_segments', ctypes.c_int32), ('reserved', ctypes.c_int32),
+        ('dst_bf16', ctypes.c_void_p), ('dstride_b', ctypes.c_int64), ('dstride_h', ctypes.c_int64),
+        ('dstride_s', ctypes.c_int64),
     ]
 
 
@@ -89,6 +112,13 @@ def lib() -> ctypes.CDLL:
                                       i32, i32, i32, i32, i32, ctypes.c_float, vp, vp, sz, i32, vp, vp]
     L.adacode_copy_to_host.restype = i32
     L.adacode_copy_to_host.argtypes = [vp, vp, sz, vp]
+    L.adacode_max_jobs.restype = i32
+    L.adacode_debug_set_wait_limit.restype = i32
+    L.adacode_debug_set_wait_limit.argtypes = [ctypes.c_uint, i32]
+    L.adacode_pack_jobs.restype = i32
+    L.adacode_pack_jobs.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, sz, vp, vp]
+    L.adacode_unpack_jobs.restype = i32
+    L.adacode_unpack_jobs.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp]
     _lib = L
     return L
 

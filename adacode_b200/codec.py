@@ -98,12 +98,24 @@ def check_device_status(device) -> None:
     word = int(read_back(s.status)[0])
     if word:
         s.status.zero_()
-        problems = []
-        if word & _lib.STATUS_ESCAPE_OVERFLOW:
-            problems.append('escape buffer too small during pack')
-        if word & _lib.STATUS_ESCAPE_UNDERRUN:
-            problems.append('escape list shorter than the code plane requires during unpack')
-        raise _lib.AdacodeError('device status: ' + '; '.join(problems))
+        raise _lib.AdacodeError('device status: ' + describe_status(word))
+
+
+_STATUS_TEXT = (
+    (_lib.STATUS_ESCAPE_OVERFLOW, 'escape buffer too small during pack'),
+    (_lib.STATUS_ESCAPE_UNDERRUN, 'escape list shorter than the code plane requires during unpack'),
+    (_lib.STATUS_TIMEOUT, 'a bounded on-chip wait gave up (results of that launch are invalid)'),
+    (_lib.STATUS_MISALIGNED, 'a plane pointer in a segment record is not 16-byte aligned (tile skipped)'),
+)
+
+
+def describe_status(word: int) -> str:
+    """Text for the bits of a device status word (every bit is named; unknown bits are shown in hex)."""
+    parts = [text for bit, text in _STATUS_TEXT if word & bit]
+    rest = word & ~sum(bit for bit, _ in _STATUS_TEXT)
+    if rest:
+        parts.append(f'unknown status bits {rest:#x}')
+    return '; '.join(parts) if parts else 'ok'
 
 
 # --------------------------------------------------------------------------------------
@@ -319,7 +331,7 @@ def _default_escape_capacity(n: int) -> int:
 
 def pack_blocks_launch(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 128, need_hist: bool = False,
                        hist_out: Optional[torch.Tensor] = None, escape_capacity: Optional[int] = None,
-                       meta_out: Optional[torch.Tensor] = None) -> _PendingPack:
+                       meta_out: Optional[torch.Tensor] = None, launch: bool = True) -> _PendingPack:
     """Start packing ``x`` (see ``pack_blocks``) and return without reading anything back.
     ``meta_out``: zeroed int64[n_blocks + 2] device buffer for the segment offsets and the status
     word (e.g. a slice of a buffer that several launches share, so that one ``read_back`` serves
@@ -349,7 +361,8 @@ def pack_blocks_launch(x: torch.Tensor, right: int, nbits: int, seq_tile: int = 
     if need_hist:
         p.hist = hist_out if hist_out is not None else torch.zeros(256, dtype=torch.int32, device=dev)
     p.cap = min(int(escape_capacity), max(n, 1)) if escape_capacity is not None else _default_escape_capacity(n)
-    p.escapes = _pack_launch(p, p.cap, p.hist)
+    if launch:
+        p.escapes = _pack_launch(p, p.cap, p.hist)
     return p
 
 
@@ -369,6 +382,31 @@ def _pack_launch(p: _PendingPack, capacity: int, hist_t) -> torch.Tensor:
     return esc
 
 
+def _pack_launch_jobs(ps: Sequence[_PendingPack]) -> None:
+    """One ``adacode_pack_jobs`` launch for pending packs of one shape and code length (the keys and
+    the values of a span); every pack gets its own escape buffer, the status word is the first one's."""
+    first = ps[0]
+    dev = first.dev
+    sc = _scratch_for(dev)
+    n_tiles = sum(p.B * p.H * p.n_blocks for p in ps)
+    ws = sc.workspace_for(n_tiles, first.seq_tile * first.D)
+    jobs = (_lib.PackJob * len(ps))()
+    for jb, p in zip(jobs, ps):
+        p.escapes = torch.empty(p.cap, dtype=torch.uint8, device=dev)
+        sb, sh, ss, _ = p.x.stride()
+        jb.src_bf16, jb.stride_b, jb.stride_h, jb.stride_s = p.x.data_ptr(), sb, sh, ss
+        jb.n_blocks, jb.right = p.n_blocks, p.right
+        jb.sign_mant, jb.codes, jb.escapes = p.sign_mant.data_ptr(), p.codes.data_ptr(), p.escapes.data_ptr()
+        jb.escapes_capacity = p.cap
+        jb.tile_base, jb.seg_escape_offsets = p.tile_base.data_ptr(), p.meta.data_ptr()
+        jb.hist256 = 0 if p.hist is None else p.hist.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_pack_jobs(
+            ctypes.addressof(jobs), len(ps), first.B, first.H, first.seq_tile, first.D, first.nbits,
+            ws.data_ptr(), ws.numel(), first.meta.data_ptr() + 8 * (first.n_blocks + 1), _stream_ptr(dev))
+    _lib.check(rc, 'adacode_pack_jobs')
+
+
 def pack_blocks_finish(p: _PendingPack, host_meta):
     """Finish a launch given the host copy of its ``meta`` (int64[n_blocks + 2]): re-run with the
     exact capacity if the escape buffer was too small, trim it, build the ``PackedChunk``."""
@@ -377,14 +415,17 @@ def pack_blocks_finish(p: _PendingPack, host_meta):
     total = offsets[-1]
     status = int(host_meta[n_blocks + 1]) & 0xFFFFFFFF
     escapes = p.escapes
-    if total > p.cap or (status & _lib.STATUS_ESCAPE_OVERFLOW):
+    # the kernels flag an overflow exactly when a stream does not fit its buffer; packs that shared
+    # a launch share the status word, so each one decides by its own total
+    status_other = status & ~_lib.STATUS_ESCAPE_OVERFLOW
+    if total > p.cap:
         p.meta.zero_()
         escapes = _pack_launch(p, total, None)   # histogram already complete from the first pass
         host = read_back(p.meta)
         if int(host[n_blocks + 1]) & 0xFFFFFFFF:
             raise _lib.AdacodeError('adacode_pack_tiles: escape overflow after re-run with exact capacity')
-    elif status:
-        raise _lib.AdacodeError(f'adacode_pack_tiles: device status {status:#x}')
+    elif status_other:
+        raise _lib.AdacodeError(f'adacode_pack_tiles: device status {status:#x} ({describe_status(status)})')
     if escapes.numel() > 2 * total + 65536:
         escapes = escapes[:total].clone()
     else:
@@ -423,9 +464,19 @@ def pack_pair(k: torch.Tensor, v: torch.Tensor, k_params, v_params, seq_tile: in
     if need_hist:
         h = mail[nk + nv:].view(torch.int32)
         k_hist, v_hist = h[:256], h[256:]
-    pk = pack_blocks_launch(k, k_params[0], k_params[1], seq_tile, need_hist, k_hist, capacities[0], mail[:nk])
-    pv = pack_blocks_launch(v, v_params[0], v_params[1], seq_tile, need_hist, v_hist, capacities[1], mail[nk:nk + nv])
+    # keys and values of one shape and code length go through ONE launch (their windows may differ)
+    together = (tuple(k.shape) == tuple(v.shape) and int(k_params[1]) == int(v_params[1]) and k.numel() > 0
+                and k.shape[-1] % 8 == 0 and 2 * k.numel() < 2 ** 31)
+    pk = pack_blocks_launch(k, k_params[0], k_params[1], seq_tile, need_hist, k_hist, capacities[0], mail[:nk],
+                            launch=not together)
+    pv = pack_blocks_launch(v, v_params[0], v_params[1], seq_tile, need_hist, v_hist, capacities[1],
+                            mail[nk:nk + nv], launch=not together)
+    if together:
+        _pack_launch_jobs([pk, pv])
     host = read_back(mail)
+    if together:
+        # one status word (the keys') serves both packs
+        host[nk + nv - 1] = int(host[nk + nv - 1]) | int(host[nk - 1])
     k_chunk, _ = pack_blocks_finish(pk, host[:nk])
     v_chunk, _ = pack_blocks_finish(pv, host[nk:nk + nv])
     kh = vh = None
@@ -559,6 +610,42 @@ def unpack_segments(segments: Sequence[TiledCompressedTensor], dst: torch.Tensor
         rc = _lib.lib().adacode_unpack_segments(table.data_ptr(), len(segments), B, H, T, D, dst.data_ptr(),
                                                 db, dh, ds, sc.status.data_ptr(), _stream_ptr(dev))
     _lib.check(rc, 'adacode_unpack_segments')
+
+
+def unpack_segments_multi(jobs: Sequence[tuple]) -> None:
+    """Unpack several segment lists, each into its own destination, with ONE launch when they
+    share [batch, kv_heads, seq_tile, head_dim] (the keys and the values of a layer).
+    ``jobs``: ``(segments, dst, table_or_None)`` tuples; anything that does not fit one launch
+    falls back to one ``unpack_segments`` call per entry."""
+    jobs = [j for j in jobs if j[0]]
+    if not jobs:
+        return
+    shape0 = tuple(jobs[0][0][0].original_shape)
+    same = all(tuple(seg.original_shape) == shape0 for segs, _, _ in jobs for seg in (segs[0], segs[-1]))
+    if len(jobs) == 1 or not same or len(jobs) > int(_lib.lib().adacode_max_jobs()):
+        for segs, dst, table in jobs:
+            unpack_segments(segs, dst, table=table)
+        return
+    B, H, T, D = shape0
+    dev = jobs[0][1].device
+    sc = _scratch_for(dev)
+    arr = (_lib.UnpackJob * len(jobs))()
+    keep = []
+    for rec, (segs, dst, table) in zip(arr, jobs):
+        for seg in segs:
+            if tuple(seg.original_shape) != shape0:
+                raise ValueError('all segments of one call must share [batch, kv_heads, seq_tile, head_dim]')
+        _check_dst(dst, B, H, D, 0)
+        if table is None:
+            table = build_segment_table(segs, None, dev)
+        keep.append(table)
+        db, dh, ds, _ = dst.stride()
+        rec.segments_dev, rec.n_segments = table.data_ptr(), len(segs)
+        rec.dst_bf16, rec.dstride_b, rec.dstride_h, rec.dstride_s = dst.data_ptr(), db, dh, ds
+    with torch.cuda.device(dev):
+        rc = _lib.lib().adacode_unpack_jobs(ctypes.addressof(arr), len(jobs), B, H, T, D, sc.status.data_ptr(),
+                                            _stream_ptr(dev))
+    _lib.check(rc, 'adacode_unpack_jobs')
 
 
 def exponent_hist(x: torch.Tensor, hist_out: Optional[torch.Tensor] = None) -> torch.Tensor:

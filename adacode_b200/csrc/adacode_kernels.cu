@@ -619,6 +619,35 @@ size_t unit_counts_bytes(int64_t n_tiles, int64_t tile_elems) {
     return align_up((size_t)n_tiles * (size_t)(tile_elems / 128 + 1) * 4, 256);
 }
 
+// Layout of the pack scratch: [completion counter, 256 B][tile_counts int32][unit_counts int32]
+// [block offsets int64, one more than blocks][escape slots, tile_elems bytes per tile].
+struct PackScratch {
+    unsigned int *done;
+    int32_t *tile_counts;
+    int32_t *unit_counts;
+    int64_t *blk_off;
+    uint8_t *esc;
+    size_t bytes;
+};
+
+PackScratch carve_pack_scratch(void *workspace, int64_t n_tiles, int64_t tile_elems) {
+    uint8_t *ws = (uint8_t *)workspace;
+    PackScratch p;
+    size_t off = 0;
+    p.done = (unsigned int *)(ws + off);
+    off += 256;
+    p.tile_counts = (int32_t *)(ws + off);
+    off += align_up((size_t)n_tiles * 4, 256);
+    p.unit_counts = (int32_t *)(ws + off);
+    off += unit_counts_bytes(n_tiles, tile_elems);
+    p.blk_off = (int64_t *)(ws + off);
+    off += align_up((size_t)(n_tiles + 2) * 8, 256);     // a launch has at most as many blocks as tiles
+    p.esc = ws + off;
+    off += (size_t)n_tiles * (size_t)tile_elems;
+    p.bytes = off;
+    return p;
+}
+
 int grid_for(int64_t n_tiles, int ctas_per_sm) {
     const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
     return (int)(n_tiles < cap ? n_tiles : cap);
@@ -650,19 +679,33 @@ int ensure_dynamic_smem(Kernel kernel, size_t bytes) {
     return ADACODE_OK;
 }
 
-int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
+// bound of the on-chip waits and the testing aid of adacode_debug_set_wait_limit
+uint32_t g_poll_limit = kMaxPolls;
+int g_withhold_unit = -1;
+
+int launch_unpack_pipe(UnpackJobsArgs &ja, cudaStream_t st) {
+    ja.poll_limit = g_poll_limit;
+    ja.withhold_unit = g_withhold_unit;
     int rc = ensure_dynamic_smem(k_unpack_pipe, sizeof(UnpackSmem));
     if (rc != ADACODE_OK) return rc;
-    const int grid = grid_for(a.n_tiles, 2);
-    k_unpack_pipe<<<grid, kPipeThreads, sizeof(UnpackSmem), st>>>(a);
+    const int grid = grid_for(ja.tile0[ja.n_jobs], 2);
+    k_unpack_pipe<<<grid, kPipeThreads, sizeof(UnpackSmem), st>>>(ja);
     ADACODE_CUDA_TRY(cudaGetLastError());
     return ADACODE_OK;
 }
 
+int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
+    UnpackJobsArgs ja;
+    ja.job[0] = a;
+    ja.tile0[0] = 0, ja.tile0[1] = a.n_tiles;
+    ja.n_jobs = 1;
+    return launch_unpack_pipe(ja, st);
+}
+
 template <int N>
-int launch_pack_pipe_n(const PackPipeArgs &pa, cudaStream_t st) {
-    const int grid = grid_for(pa.base.n_tiles, 2);
-    if (pa.base.hist) {
+int launch_pack_pipe_n(const PackPipeArgs &pa, bool hist, cudaStream_t st) {
+    const int grid = grid_for(pa.n_tiles, 2);
+    if (hist) {
         int rc = ensure_dynamic_smem(k_pack_pipe<N, true>, sizeof(PackSmem));
         if (rc != ADACODE_OK) return rc;
         k_pack_pipe<N, true><<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
@@ -675,13 +718,31 @@ int launch_pack_pipe_n(const PackPipeArgs &pa, cudaStream_t st) {
     return ADACODE_OK;
 }
 
+// Pipelined pack of all jobs of `pa` with one pack launch and one compaction launch.
 int launch_pack_pipe(const PackPipeArgs &pa, int nbits, cudaStream_t st) {
-    switch (nbits) {
-        case 1: return launch_pack_pipe_n<1>(pa, st);
-        case 2: return launch_pack_pipe_n<2>(pa, st);
-        case 3: return launch_pack_pipe_n<3>(pa, st);
-        default: return launch_pack_pipe_n<4>(pa, st);
+    bool hist = false;
+    int max_blocks = 0;
+    for (int j = 0; j < pa.n_jobs; ++j) {
+        hist = hist || pa.job[j].hist != nullptr;
+        max_blocks = pa.job[j].n_blocks > max_blocks ? pa.job[j].n_blocks : max_blocks;
     }
+    int rc;
+    switch (nbits) {
+        case 1: rc = launch_pack_pipe_n<1>(pa, hist, st); break;
+        case 2: rc = launch_pack_pipe_n<2>(pa, hist, st); break;
+        case 3: rc = launch_pack_pipe_n<3>(pa, hist, st); break;
+        default: rc = launch_pack_pipe_n<4>(pa, hist, st); break;
+    }
+    if (rc != ADACODE_OK) return rc;
+    // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
+    const int64_t job_tiles = (int64_t)max_blocks * pa.BH;
+    const int64_t want = (job_tiles + kWarps - 1) / kWarps;
+    const int64_t cap = ((int64_t)sm_count() * 4 + pa.n_jobs - 1) / pa.n_jobs;
+    const dim3 cgrid((unsigned)(want < cap ? want : cap), (unsigned)pa.n_jobs);
+    if (hist) k_compact_units<true><<<cgrid, kThreads, 0, st>>>(pa);
+    else k_compact_units<false><<<cgrid, kThreads, 0, st>>>(pa);
+    ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
 }
 
 template <int N, int CH>
@@ -738,83 +799,38 @@ int adacode_copy_to_host(const void *src_dev, void *dst_host_pinned, size_t byte
 
 size_t adacode_pack_workspace_bytes(int64_t n_tiles, int64_t tile_elems) {
     if (n_tiles <= 0 || tile_elems <= 0) return 256;
-    // [done counter, padded to 256][tile_counts int32][unit_counts int32][escape scratch]
     // a tile has at most tile_elems / 128 units (a unit is at least 8 rows of at least 16 elements)
-    return 256 + align_up((size_t)n_tiles * 4, 256) + unit_counts_bytes(n_tiles, tile_elems) +
-           (size_t)n_tiles * (size_t)tile_elems;
+    return carve_pack_scratch(nullptr, n_tiles, tile_elems).bytes;
 }
 
-int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s, int B, int H,
-                       int n_blocks, int seq_tile, int D, int right, int nbits, uint8_t *sign_mant, uint8_t *codes,
-                       uint8_t *escapes, int64_t escapes_capacity, int32_t *tile_base, int64_t *seg_escape_offsets,
-                       int32_t *hist256, void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
-    if (B < 0 || H < 0 || n_blocks < 0 || seq_tile <= 0 || D <= 0) return ADACODE_ERR_INVALID_ARG;
-    if (nbits < 1 || nbits > 4 || D % 8 != 0) return ADACODE_ERR_INVALID_ARG;
-    if (!seg_escape_offsets || !status || escapes_capacity < 0) return ADACODE_ERR_INVALID_ARG;
-    const int64_t n_tiles = (int64_t)B * H * n_blocks;
-    const int64_t tile_elems = (int64_t)seq_tile * D;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (n_tiles == 0) {
-        ADACODE_CUDA_TRY(cudaMemsetAsync(seg_escape_offsets, 0, sizeof(int64_t) * (size_t)(n_blocks + 1), st));
-        return ADACODE_OK;
-    }
-    if (n_tiles * tile_elems >= (1ll << 31)) return ADACODE_ERR_TOO_LARGE;
-    if (!src_bf16 || !sign_mant || !codes || !tile_base || !workspace || (!escapes && escapes_capacity > 0))
-        return ADACODE_ERR_INVALID_ARG;
-    if ((((uintptr_t)src_bf16 | (uintptr_t)sign_mant | (uintptr_t)codes | (uintptr_t)workspace) & 15) != 0)
-        return ADACODE_ERR_INVALID_ARG;
-    if ((stride_b | stride_h | stride_s) & 7) return ADACODE_ERR_INVALID_ARG;
-    if (workspace_bytes < adacode_pack_workspace_bytes(n_tiles, tile_elems)) return ADACODE_ERR_WORKSPACE;
+}  // extern "C"
 
+namespace {
+
+// The direct (not pipelined) kernels, one job: shapes the bulk-copy pipeline does not take.
+int pack_direct(const adacode_pack_job &jb, int B, int H, int seq_tile, int D, int nbits, const PackScratch &sc,
+                int32_t *status, cudaStream_t st) {
+    const int64_t n_tiles = (int64_t)B * H * jb.n_blocks;
+    const int64_t tile_elems = (int64_t)seq_tile * D;
     const int CH = (D % 16 == 0) ? 16 : 8;
-    uint8_t *ws = (uint8_t *)workspace;
     PackArgs a;
-    a.src = (const uint16_t *)src_bf16;
-    a.sb = stride_b, a.sh = stride_h, a.ss = stride_s;
+    a.src = (const uint16_t *)jb.src_bf16;
+    a.sb = jb.stride_b, a.sh = jb.stride_h, a.ss = jb.stride_s;
     a.H = H, a.BH = B * H, a.seq_tile = seq_tile, a.D = D;
-    a.left = right - (1 << nbits) + 1;
+    a.left = jb.right - (1 << nbits) + 1;
     a.n_tiles = n_tiles;
     a.tile_elems = (int)tile_elems;
     a.chunks_per_tile = (int)(tile_elems / CH);
     a.tile_code_bytes = (int)(tile_elems * nbits / 8);
-    a.sign_mant = sign_mant;
-    a.codes = codes;
-    a.done = (unsigned int *)ws;
-    a.tile_counts = (int32_t *)(ws + 256);
-    int32_t *unit_counts = (int32_t *)(ws + 256 + align_up((size_t)n_tiles * 4, 256));
-    a.esc_scratch = ws + 256 + align_up((size_t)n_tiles * 4, 256) + unit_counts_bytes(n_tiles, tile_elems);
-    a.tile_base = tile_base;
-    a.seg_off = seg_escape_offsets;
-    a.n_blocks = n_blocks;
-    a.hist = hist256;
-
-    // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
-    const int cgrid = (int)((n_tiles + kWarps - 1) / kWarps < (int64_t)sm_count() * 4
-                                ? (n_tiles + kWarps - 1) / kWarps
-                                : (int64_t)sm_count() * 4);
-    // (the pipelined kernel counts histogram hits in 16-bit fields per thread: keep tiles below 2**24 elements)
-    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D) && tile_elems <= (1 << 24)) {
-        PackPipeArgs pa;
-        pa.base = a;
-        pa.unit_counts = unit_counts;
-        pa.unit_rows = unit_rows_for(seq_tile, D);
-        pa.units_per_tile = (seq_tile + pa.unit_rows - 1) / pa.unit_rows;
-        pa.status = status;
-        int rc = launch_pack_pipe(pa, nbits, st);
-        if (rc != ADACODE_OK) return rc;
-        if (hist256)
-            k_compact_units<true><<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
-                                                              seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
-                                                              pa.unit_rows * D, pa.units_per_tile, escapes,
-                                                              escapes_capacity, hist256, status);
-        else
-            k_compact_units<false><<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, unit_counts, tile_base,
-                                                               seg_escape_offsets, n_tiles, a.BH, a.tile_elems,
-                                                               pa.unit_rows * D, pa.units_per_tile, escapes,
-                                                               escapes_capacity, nullptr, status);
-        ADACODE_CUDA_TRY(cudaGetLastError());
-        return ADACODE_OK;
-    }
+    a.sign_mant = jb.sign_mant;
+    a.codes = jb.codes;
+    a.done = sc.done;
+    a.tile_counts = sc.tile_counts;
+    a.esc_scratch = sc.esc;
+    a.tile_base = jb.tile_base;
+    a.seg_off = jb.seg_escape_offsets;
+    a.n_blocks = jb.n_blocks;
+    a.hist = jb.hist256;
     const int grid = grid_for(n_tiles, 4);
     if (CH == 16) {
         switch (nbits) {
@@ -832,10 +848,117 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
         }
     }
     ADACODE_CUDA_TRY(cudaGetLastError());
-    k_compact_escapes<<<cgrid, kThreads, 0, st>>>(a.esc_scratch, a.tile_counts, tile_base, seg_escape_offsets,
-                                                  n_tiles, a.BH, a.tile_elems, escapes, escapes_capacity, status);
+    const int64_t want = (n_tiles + kWarps - 1) / kWarps;
+    const int64_t cap = (int64_t)sm_count() * 4;
+    k_compact_escapes<<<(int)(want < cap ? want : cap), kThreads, 0, st>>>(
+        a.esc_scratch, a.tile_counts, jb.tile_base, jb.seg_escape_offsets, n_tiles, a.BH, a.tile_elems, jb.escapes,
+        jb.escapes_capacity, status);
     ADACODE_CUDA_TRY(cudaGetLastError());
     return ADACODE_OK;
+}
+
+int pack_jobs_impl(const adacode_pack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D, int nbits,
+                   void *workspace, size_t workspace_bytes, int32_t *status, cudaStream_t st) {
+    if (n_jobs < 0 || n_jobs > kMaxJobs || (n_jobs > 0 && !jobs)) return ADACODE_ERR_INVALID_ARG;
+    if (B < 0 || H < 0 || seq_tile <= 0 || D <= 0) return ADACODE_ERR_INVALID_ARG;
+    if (nbits < 1 || nbits > 4 || D % 8 != 0 || !status) return ADACODE_ERR_INVALID_ARG;
+    const int64_t tile_elems = (int64_t)seq_tile * D;
+    const int64_t BH = (int64_t)B * H;
+    int64_t n_tiles = 0, max_job_tiles = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        const adacode_pack_job &jb = jobs[j];
+        if (jb.n_blocks < 0 || !jb.seg_escape_offsets || jb.escapes_capacity < 0) return ADACODE_ERR_INVALID_ARG;
+        const int64_t jt = BH * jb.n_blocks;
+        if (jt == 0) continue;
+        if (!jb.src_bf16 || !jb.sign_mant || !jb.codes || !jb.tile_base || (!jb.escapes && jb.escapes_capacity > 0))
+            return ADACODE_ERR_INVALID_ARG;
+        if ((((uintptr_t)jb.src_bf16 | (uintptr_t)jb.sign_mant | (uintptr_t)jb.codes) & 15) != 0)
+            return ADACODE_ERR_INVALID_ARG;
+        if ((jb.stride_b | jb.stride_h | jb.stride_s) & 7) return ADACODE_ERR_INVALID_ARG;
+        n_tiles += jt;
+        max_job_tiles = jt > max_job_tiles ? jt : max_job_tiles;
+    }
+    for (int j = 0; j < n_jobs; ++j)
+        if (BH * jobs[j].n_blocks == 0)
+            ADACODE_CUDA_TRY(cudaMemsetAsync(jobs[j].seg_escape_offsets, 0,
+                                             sizeof(int64_t) * (size_t)(jobs[j].n_blocks + 1), st));
+    if (n_tiles == 0) return ADACODE_OK;
+    if (n_tiles * tile_elems >= (1ll << 31)) return ADACODE_ERR_TOO_LARGE;
+    if (!workspace || ((uintptr_t)workspace & 15) != 0) return ADACODE_ERR_INVALID_ARG;
+
+    // (the pipelined kernel's unit bookkeeping is 32-bit: keep tiles below 2**24 elements)
+    if (pipeline_enabled() && pipeline_shape_ok(seq_tile, D) && tile_elems <= (1 << 24)) {
+        if (workspace_bytes < adacode_pack_workspace_bytes(n_tiles, tile_elems)) return ADACODE_ERR_WORKSPACE;
+        const PackScratch sc = carve_pack_scratch(workspace, n_tiles, tile_elems);
+        PackPipeArgs pa;
+        memset(&pa, 0, sizeof(pa));
+        int64_t tile0 = 0;
+        int blk0 = 0, n = 0;
+        for (int j = 0; j < n_jobs; ++j) {
+            const adacode_pack_job &jb = jobs[j];
+            if (BH * jb.n_blocks == 0) continue;
+            PackJob &d = pa.job[n++];
+            d.src = (const uint16_t *)jb.src_bf16;
+            d.sb = jb.stride_b, d.sh = jb.stride_h, d.ss = jb.stride_s;
+            d.sign_mant = jb.sign_mant, d.codes = jb.codes, d.escapes = jb.escapes;
+            d.capacity = jb.escapes_capacity;
+            d.tile_base = jb.tile_base, d.seg_off = jb.seg_escape_offsets, d.hist = jb.hist256;
+            d.tile0 = tile0, d.blk0 = blk0, d.n_blocks = jb.n_blocks;
+            d.left = jb.right - (1 << nbits) + 1;
+            tile0 += BH * jb.n_blocks;
+            blk0 += jb.n_blocks;
+        }
+        pa.n_jobs = n;
+        pa.H = H, pa.BH = (int)BH, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = (int)tile_elems;
+        pa.n_tiles = n_tiles;
+        pa.esc_scratch = sc.esc, pa.tile_counts = sc.tile_counts, pa.unit_counts = sc.unit_counts;
+        pa.blk_off = sc.blk_off, pa.done = sc.done;
+        pa.unit_rows = unit_rows_for(seq_tile, D);
+        pa.units_per_tile = (seq_tile + pa.unit_rows - 1) / pa.unit_rows;
+        pa.status = status;
+        pa.poll_limit = g_poll_limit;
+        return launch_pack_pipe(pa, nbits, st);
+    }
+    if (workspace_bytes < adacode_pack_workspace_bytes(max_job_tiles, tile_elems)) return ADACODE_ERR_WORKSPACE;
+    const PackScratch sc = carve_pack_scratch(workspace, max_job_tiles, tile_elems);
+    for (int j = 0; j < n_jobs; ++j) {
+        if (BH * jobs[j].n_blocks == 0) continue;
+        const int rc = pack_direct(jobs[j], B, H, seq_tile, D, nbits, sc, status, st);
+        if (rc != ADACODE_OK) return rc;
+    }
+    return ADACODE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int adacode_pack_jobs(const adacode_pack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D, int nbits,
+                      void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
+    return pack_jobs_impl(jobs, n_jobs, B, H, seq_tile, D, nbits, workspace, workspace_bytes, status,
+                          (cudaStream_t)stream);
+}
+
+int adacode_max_jobs(void) { return kMaxJobs; }
+
+int adacode_debug_set_wait_limit(unsigned int polls, int withhold_unit) {
+    g_poll_limit = polls == 0 ? kMaxPolls : polls;
+    g_withhold_unit = withhold_unit;
+    return ADACODE_OK;
+}
+
+int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s, int B, int H,
+                       int n_blocks, int seq_tile, int D, int right, int nbits, uint8_t *sign_mant, uint8_t *codes,
+                       uint8_t *escapes, int64_t escapes_capacity, int32_t *tile_base, int64_t *seg_escape_offsets,
+                       int32_t *hist256, void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
+    adacode_pack_job jb;
+    jb.src_bf16 = src_bf16;
+    jb.stride_b = stride_b, jb.stride_h = stride_h, jb.stride_s = stride_s;
+    jb.n_blocks = n_blocks, jb.right = right;
+    jb.sign_mant = sign_mant, jb.codes = codes, jb.escapes = escapes;
+    jb.escapes_capacity = escapes_capacity;
+    jb.tile_base = tile_base, jb.seg_escape_offsets = seg_escape_offsets, jb.hist256 = hist256;
+    return pack_jobs_impl(&jb, 1, B, H, seq_tile, D, nbits, workspace, workspace_bytes, status, (cudaStream_t)stream);
 }
 
 static int check_unpack_common(int B, int H, int seq_tile, int D, const void *dst, int64_t db, int64_t dh,
@@ -917,6 +1040,44 @@ int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments,
     else k_unpack_segments<8><<<grid, kThreads, 0, st>>>(u, segments_dev, n_tiles);
     ADACODE_CUDA_TRY(cudaGetLastError());
     return ADACODE_OK;
+}
+
+int adacode_unpack_jobs(const adacode_unpack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D,
+                        int32_t *status, void *stream) {
+    if (n_jobs < 0 || n_jobs > kMaxJobs || (n_jobs > 0 && !jobs)) return ADACODE_ERR_INVALID_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool pipe = pipeline_enabled() && pipeline_shape_ok(seq_tile, D);
+    UnpackJobsArgs ja;
+    memset(&ja, 0, sizeof(ja));
+    int n = 0;
+    long long tile0 = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        const adacode_unpack_job &jb = jobs[j];
+        if (jb.n_segments < 0) return ADACODE_ERR_INVALID_ARG;
+        const int64_t n_tiles = (int64_t)B * H * jb.n_segments;
+        if (n_tiles == 0) continue;
+        int rc = check_unpack_common(B, H, seq_tile, D, jb.dst_bf16, jb.dstride_b, jb.dstride_h, jb.dstride_s, status);
+        if (rc != ADACODE_OK) return rc;
+        if (!jb.segments_dev) return ADACODE_ERR_INVALID_ARG;
+        if (!pipe) {
+            rc = adacode_unpack_segments(jb.segments_dev, jb.n_segments, B, H, seq_tile, D, jb.dst_bf16, jb.dstride_b,
+                                         jb.dstride_h, jb.dstride_s, status, stream);
+            if (rc != ADACODE_OK) return rc;
+            continue;
+        }
+        UnpackPipeArgs &pa = ja.job[n];
+        pa.seg = jb.segments_dev;
+        pa.H = H, pa.BH = B * H, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = seq_tile * D;
+        pa.n_tiles = n_tiles, pa.dst = (uint16_t *)jb.dst_bf16;
+        pa.db = jb.dstride_b, pa.dh = jb.dstride_h, pa.ds = jb.dstride_s, pa.status = status;
+        ja.tile0[n] = tile0;
+        tile0 += n_tiles;
+        ++n;
+    }
+    if (!pipe || n == 0) return ADACODE_OK;
+    ja.tile0[n] = tile0;
+    ja.n_jobs = n;
+    return launch_unpack_pipe(ja, st);
 }
 
 int adacode_hist_bf16(const void *src_bf16, int64_t stride_b, int64_t stride_h, int64_t stride_s, int B, int H, int S,

@@ -10,6 +10,9 @@
 //                   stages the tile's escape bytes with plain loads
 //   consumer warps: wait on "full", work out of shared memory, signal "empty", and hand the
 //                   finished unit to a bulk store
+// A unit leaves through ONE bulk store per plane: the copy engine has a sizeable cost per
+// operation, and a variant in which every consumer warp stored its own 2 KB slice (no CTA-wide
+// barrier inside a unit) ran 40 % slower than this one.
 // Every mbarrier wait is bounded: after kMaxPolls failed polls the waiter records
 // ADACODE_STATUS_TIMEOUT in the status word and carries on (the result is then wrong but the
 // kernel still reaches every barrier and terminates).
@@ -53,8 +56,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ bool launch_timed_out(const int32_t *status) {
     return (*reinterpret_cast<const volatile int32_t *>(status) & ADACODE_STATUS_TIMEOUT) != 0;
 }
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status) {
-    for (uint32_t i = 0; i < kMaxPolls; ++i) {
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status,
+                                          uint32_t limit = kMaxPolls) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return;
         if ((i & 4095u) == 4095u && launch_timed_out(status)) return;
     }
@@ -155,6 +159,7 @@ struct UnitMeta {
     int left;
     int nbits;
     int first_unit_of_tile;
+    long long ds;             // destination row stride in elements
 };
 
 // bulk copies need 16-byte aligned shared addresses: every buffer starts on a 128-byte boundary
@@ -200,6 +205,7 @@ struct TileSrc {
     long long esc_len, esc_start;
     int esc_cnt, left, nbits;
     uint16_t *dst;
+    long long ds;
 };
 
 __device__ __forceinline__ TileSrc resolve_tile(const UnpackPipeArgs &a, long long tile) {
@@ -208,6 +214,7 @@ __device__ __forceinline__ TileSrc resolve_tile(const UnpackPipeArgs &a, long lo
     const int bh = (int)(tile - blk * a.BH);
     const int b = bh / a.H, h = bh - b * a.H;
     uint16_t *base = a.dst + (long long)b * a.db + (long long)h * a.dh;
+    t.ds = a.ds;
     if (a.seg) {
         const adacode_segment sg = a.seg[blk];
         t.nbits = sg.nbits, t.left = sg.left;
@@ -249,6 +256,7 @@ __device__ __forceinline__ TileSrc shfl_tile(const TileSrc &m, int src) {
     t.esc_cnt = __shfl_sync(kFull, m.esc_cnt, src);
     t.left = __shfl_sync(kFull, m.left, src), t.nbits = __shfl_sync(kFull, m.nbits, src);
     t.dst = shfl_ptr(m.dst, src);
+    t.ds = shfl_ll(m.ds, src);
     return t;
 }
 
@@ -287,7 +295,7 @@ __device__ __forceinline__ EscWindow esc_window(const TileSrc &t) {
 // the stage's meta block and start its bulk copies against `full_bar`.
 __device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, const TileSrc &t, const EscWindow &w,
                                            int row0, int rows, int D, uint16_t *dst, bool first_unit,
-                                           int32_t *status) {
+                                           int32_t *status, bool withhold = false) {
     const int lane = threadIdx.x & 31;
     if (w.tail > 0) {
         if (lane < w.tail) st.esc[w.win + lane] = w.a0[w.win + lane];
@@ -303,8 +311,14 @@ __device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, 
         m.esc_staged = w.staged, m.esc_shift = w.shift;
         m.elems = elems, m.left = t.left, m.nbits = t.nbits;
         m.first_unit_of_tile = first_unit;
+        m.ds = t.ds;
         const uint32_t cbytes = (uint32_t)elems * t.nbits / 8;
-        if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)dst) & 15) != 0 || (cbytes & 15) != 0 || t.nbits < 1 ||
+        if (withhold) {
+            // testing aid: an empty unit whose "loaded" signal never comes; the consumers' bounded
+            // wait runs out, they flag ADACODE_STATUS_TIMEOUT and carry on with nothing to do
+            m.elems = 0;
+            m.nbits = 1;
+        } else if ((((uintptr_t)src_sm | (uintptr_t)src_cd | (uintptr_t)dst) & 15) != 0 || (cbytes & 15) != 0 || t.nbits < 1 ||
             t.nbits > 4) {
             // never start a misaligned bulk copy: flag it and hand over an empty unit
             atomicOr(status, ADACODE_STATUS_MISALIGNED);
@@ -359,10 +373,11 @@ __device__ __forceinline__ void decode_chunks(const UnpackStage &st, const uint3
 
 template <int N>
 __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
-                                            int &consumed, bool rows_contig, int D, long long ds,
-                                            int32_t *status) {
+                                            int &consumed, int D, int32_t *status) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const UnitMeta m = st.meta;
+    const long long ds = m.ds;
+    const bool rows_contig = (ds == D);
     if (m.first_unit_of_tile) consumed = 0;
     const int chunks = m.elems >> 4;
 
@@ -453,10 +468,23 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     }
 }
 
-__global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPipeArgs a) {
+constexpr int kMaxJobs = 8;
+
+// Up to kMaxJobs destinations in one launch; job j owns the tiles [tile0[j], tile0[j + 1]).
+struct UnpackJobsArgs {
+    UnpackPipeArgs job[kMaxJobs];
+    long long tile0[kMaxJobs + 1];
+    int n_jobs;
+    uint32_t poll_limit;      // bound of every on-chip wait (kMaxPolls unless a test lowered it)
+    int withhold_unit;        // testing aid: CTA 0's producer never signals this unit as loaded (-1: off)
+};
+
+__global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const __grid_constant__ UnpackJobsArgs ja) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     UnpackSmem &s = *reinterpret_cast<UnpackSmem *>(smem_raw);
     const int tid = threadIdx.x;
+    const UnpackPipeArgs &a0 = ja.job[0];          // geometry and status word are common to all jobs
+    const long long n_tiles = ja.tile0[ja.n_jobs];
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
@@ -467,9 +495,8 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
     }
     __syncthreads();
 
-    const int unit_rows = unit_rows_for(a.seq_tile, a.D);
-    const int units_per_tile = (a.seq_tile + unit_rows - 1) / unit_rows;
-    const bool rows_contig = (a.ds == a.D);
+    const int unit_rows = unit_rows_for(a0.seq_tile, a0.D);
+    const int units_per_tile = (a0.seq_tile + unit_rows - 1) / unit_rows;
 
     if (tid >= kConsumerThreads) {
         // ---------------- producer warp ----------------
@@ -479,24 +506,35 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
         const int lane = tid & 31;
         uint32_t it = 0;
         const long long my_tiles =
-            a.n_tiles > (long long)blockIdx.x ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            n_tiles > (long long)blockIdx.x ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         for (long long base = 0; base < my_tiles; base += 32) {
             TileSrc mine = {};
-            if (base + lane < my_tiles) mine = resolve_tile(a, blockIdx.x + (base + lane) * (long long)gridDim.x);
+            if (base + lane < my_tiles) {
+                const long long tile = blockIdx.x + (base + lane) * (long long)gridDim.x;
+                int j = 0;
+                while (j + 1 < ja.n_jobs && tile >= ja.tile0[j + 1]) ++j;
+                mine = resolve_tile(ja.job[j], tile - ja.tile0[j]);
+            }
             const int n_here = (int)(my_tiles - base < 32 ? my_tiles - base : 32);
             for (int j = 0; j < n_here; ++j) {
                 const TileSrc t = shfl_tile(mine, j);
                 const EscWindow w = esc_window(t);
                 for (int u = 0; u < units_per_tile; ++u, ++it) {
                     const int stg = it % kStages;
-                    mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
+                    mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a0.status, ja.poll_limit);
                     const int row0 = u * unit_rows;
-                    const int rows = min(unit_rows, a.seq_tile - row0);
-                    issue_unit(s.stage[stg], &s.full[stg], t, w, row0, rows, a.D, t.dst + (long long)row0 * a.ds,
-                               u == 0, a.status);
+                    const int rows = min(unit_rows, a0.seq_tile - row0);
+                    issue_unit(s.stage[stg], &s.full[stg], t, w, row0, rows, a0.D, t.dst + (long long)row0 * t.ds,
+                               u == 0, a0.status, blockIdx.x == 0 && (int)it == ja.withhold_unit);
                 }
             }
         }
+        // Do not leave while a copy into this CTA's shared memory may still be in flight: after a
+        // timed-out launch the consumers can be ahead of the data (a bounded wait, like all others).
+        if (launch_timed_out(a0.status))
+            for (uint32_t k = it > kStages ? it - kStages : 0; k < it; ++k)
+                if (!(blockIdx.x == 0 && (int)k == ja.withhold_unit))
+                    mbar_wait(&s.full[k % kStages], (k / kStages) & 1, a0.status, ja.poll_limit);
         return;
     }
 
@@ -504,10 +542,10 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
     uint32_t it = 0;
     int consumed = 0;
     int lut_left = 0, lut_nbits = 0;      // what s.lut currently encodes (nbits 0: nothing yet)
-    for (long long tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         for (int u = 0; u < units_per_tile; ++u, ++it) {
             const int stg = it % kStages;
-            if ((tid & 31) == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, a.status);
+            if ((tid & 31) == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, a0.status, ja.poll_limit);
             __syncwarp();
             const UnpackStage &st = s.stage[stg];
             const int nb = st.meta.nbits, lf = st.meta.left;
@@ -519,10 +557,10 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const UnpackPip
                 consumer_sync();
             }
             switch (nb) {
-                case 1: unpack_unit<1>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
-                case 2: unpack_unit<2>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
-                case 3: unpack_unit<3>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
-                default: unpack_unit<4>(s, st, &s.empty[stg], consumed, rows_contig, a.D, a.ds, a.status); break;
+                case 1: unpack_unit<1>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
+                case 2: unpack_unit<2>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
+                case 3: unpack_unit<3>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
+                default: unpack_unit<4>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
             }
         }
     }
@@ -593,6 +631,7 @@ struct PackUnitMeta {
     int elems;
     int first_unit_of_tile;
     int last_unit_of_tile;
+    int job;               // index into PackPipeArgs::job
 };
 
 struct alignas(128) PackStage {
@@ -616,33 +655,62 @@ struct alignas(128) PackSmem {
 };
 static_assert(sizeof(PackStage) % 128 == 0, "stage buffers must stay 128-byte aligned");
 
-struct PackPipeArgs {
-    PackArgs base;            // the fields shared with the direct kernel
-    int32_t *unit_counts;     // n_tiles * units_per_tile
-    int unit_rows, units_per_tile;
-    int32_t *status;
+// One tensor of a pack launch.  All jobs of a launch share B, H, seq_tile, D and the code length;
+// job j owns the global tiles [tile0, tile0 + BH * n_blocks) and the global blocks [blk0, blk0 + n_blocks).
+struct PackJob {
+    const uint16_t *src;
+    int64_t sb, sh, ss;
+    uint8_t *sign_mant, *codes, *escapes;
+    int64_t capacity;
+    int32_t *tile_base;
+    int64_t *seg_off;
+    int32_t *hist;           // nullable
+    int64_t tile0;
+    int blk0, n_blocks, left, pad;
 };
 
-// Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets.
+struct PackPipeArgs {
+    PackJob job[kMaxJobs];
+    int n_jobs;
+    int H, BH, seq_tile, D, tile_elems;
+    int64_t n_tiles;          // over all jobs
+    uint8_t *esc_scratch;     // n_tiles * tile_elems bytes, global tile t owns [t * tile_elems, ...)
+    int32_t *tile_counts;     // n_tiles
+    int32_t *unit_counts;     // n_tiles * units_per_tile
+    int64_t *blk_off;         // over all blocks of the launch: escapes before global block i (n_blocks_total + 1)
+    unsigned int *done;       // zero on entry, zero on exit
+    int unit_rows, units_per_tile;
+    int32_t *status;
+    uint32_t poll_limit;      // bound of every on-chip wait (kMaxPolls unless a test lowered it)
+};
+
+__device__ __forceinline__ int job_of_tile(const PackPipeArgs &pa, int64_t tile) {
+    int j = 0;
+    while (j + 1 < pa.n_jobs && tile >= pa.job[j + 1].tile0) ++j;
+    return j;
+}
+
+// Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets (per job).
 // Run by the consumer threads of the CTA that finished last, while the rest of the GPU is idle,
 // so it is kept short: every thread takes a run of kScanRun consecutive tiles, fetches their
 // counts with independent loads (one memory round trip per pass of 512 x kScanRun tiles), and
 // one block scan of the run totals gives every tile its prefix.
 constexpr int kScanRun = 8;
 
-__device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s_carry, int *s_scan) {
+__device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long long *s_carry, int *s_scan) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         *s_carry = 0;
-        a.seg_off[0] = 0;
+        pa.blk_off[0] = 0;
     }
+    if (tid < pa.n_jobs) pa.job[tid].seg_off[0] = 0;
     consumer_sync();
     const int64_t per_pass = (int64_t)kConsumerThreads * kScanRun;
-    for (int64_t pass = 0; pass < a.n_tiles; pass += per_pass) {
+    for (int64_t pass = 0; pass < pa.n_tiles; pass += per_pass) {
         const int64_t t0 = pass + (int64_t)tid * kScanRun;
         int c[kScanRun];
 #pragma unroll
-        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < a.n_tiles) ? __ldcg(a.tile_counts + t0 + i) : 0;
+        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < pa.n_tiles) ? __ldcg(pa.tile_counts + t0 + i) : 0;
         int run = 0;
 #pragma unroll
         for (int i = 0; i < kScanRun; ++i) run += c[i];
@@ -662,30 +730,48 @@ __device__ __forceinline__ void scan_tile_counts(const PackArgs &a, long long *s
             tot += v;
         }
         long long incl = *s_carry + wp + (x - run);       // escapes before this thread's run
+        long long inc[kScanRun];
 #pragma unroll
         for (int i = 0; i < kScanRun; ++i) {
             const int64_t t = t0 + i;
             incl += c[i];
-            c[i] = (int)incl;                             // inclusive prefix over the whole call
-            if (t < a.n_tiles && (t + 1) % a.BH == 0) a.seg_off[(t + 1) / a.BH] = incl;
+            inc[i] = incl;                                // inclusive prefix over the whole launch
+            if (t < pa.n_tiles && (t + 1) % pa.BH == 0) pa.blk_off[(t + 1) / pa.BH] = incl;
         }
-        consumer_sync();                                  // segment offsets of this pass are written
+        consumer_sync();                                  // block offsets up to the end of this pass are written
         if (tid == 0) *s_carry += tot;
 #pragma unroll
         for (int i = 0; i < kScanRun; ++i) {
             const int64_t t = t0 + i;
-            if (t < a.n_tiles) {
-                const int64_t blk = t / a.BH;
-                a.tile_base[t] = c[i] - (blk > 0 ? (int)a.seg_off[blk] : 0);
+            if (t < pa.n_tiles) {
+                const int64_t gb = t / pa.BH;
+                const PackJob &jb = pa.job[job_of_tile(pa, t)];
+                jb.tile_base[t - jb.tile0] = (int32_t)(inc[i] - pa.blk_off[gb]);
+                if ((t + 1) % pa.BH == 0) jb.seg_off[gb + 1 - jb.blk0] = inc[i] - pa.blk_off[jb.blk0];
             }
         }
         consumer_sync();
     }
-    if (tid == 0) *a.done = 0u;
+    if (tid == 0) *pa.done = 0u;
+}
+
+// Per-thread in-window counters (16-bit fields) -> the CTA's shared histogram.
+template <int N>
+__device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::v], int left, int *s_hist) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int v = 1; v < (1 << N); ++v) {
+        const uint32_t mine = (cnt2[v >> 1] >> (16 * (v & 1))) & 0xFFFFu;
+        const uint32_t sum = __reduce_add_sync(kFull, mine);
+        const int bin = left + v;
+        if (lane == 0 && sum != 0 && bin >= 0 && bin < 256) atomicAdd(&s_hist[bin], (int)sum);
+    }
+#pragma unroll
+    for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
 }
 
 template <int N, bool HIST>
-__device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint64_t *empty_bar, int left,
+__device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint64_t *empty_bar,
                                           int &running, uint32_t (&cnt2)[HistRegs<N>::v]) {
     constexpr int CB = 2 * N;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -785,10 +871,9 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
 }
 
 template <int N, bool HIST>
-__global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArgs pa) {
+__global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_constant__ PackPipeArgs pa) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     PackSmem &s = *reinterpret_cast<PackSmem *>(smem_raw);
-    const PackArgs &a = pa.base;
     const int tid = threadIdx.x;
     if (tid == 0) {
 #pragma unroll
@@ -799,54 +884,58 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (HIST && tid < 256) s.hist[tid] = 0;
-    if (tid < 256) {
-        const uint32_t code = (uint32_t)tid - (uint32_t)a.left;
-        s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
-    }
     __syncthreads();
 
     const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
-    const bool rows_contig = (a.ss == a.D);
 
     if (tid >= kConsumerThreads) {
         // ---------------- producer warp ----------------
         const int lane = tid & 31;
         uint32_t it = 0;
-        for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
-            const int64_t blk = tile / a.BH;
-            const int bh = (int)(tile - blk * a.BH);
-            const int b = bh / a.H, h = bh - b * a.H;
-            const uint16_t *tsrc = a.src + (int64_t)b * a.sb + (int64_t)h * a.sh + blk * a.seq_tile * a.ss;
+        for (int64_t tile = blockIdx.x; tile < pa.n_tiles; tile += gridDim.x) {
+            const int j = job_of_tile(pa, tile);
+            const PackJob &jb = pa.job[j];
+            const int64_t lt = tile - jb.tile0;
+            const int64_t blk = lt / pa.BH;
+            const int bh = (int)(lt - blk * pa.BH);
+            const int b = bh / pa.H, h = bh - b * pa.H;
+            const uint16_t *tsrc = jb.src + (int64_t)b * jb.sb + (int64_t)h * jb.sh + blk * pa.seq_tile * jb.ss;
+            const bool rows_contig = (jb.ss == pa.D);
             for (int u = 0; u < upt; ++u, ++it) {
                 const int stg = it % kStages;
                 PackStage &st = s.stage[stg];
-                mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, pa.status);
+                mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, pa.status, pa.poll_limit);
                 const int row0 = u * unit_rows;
-                const int rows = min(unit_rows, a.seq_tile - row0);
-                const int elems = rows * a.D;
+                const int rows = min(unit_rows, pa.seq_tile - row0);
+                const int elems = rows * pa.D;
                 if (lane == 0) {
                     PackUnitMeta &m = st.meta;
-                    const int64_t e0 = tile * a.tile_elems + (int64_t)row0 * a.D;
-                    m.sm_dst = a.sign_mant + e0;
-                    m.code_dst = a.codes + e0 * N / 8;
-                    m.esc_dst = a.esc_scratch + e0;
+                    const int64_t e0 = lt * pa.tile_elems + (int64_t)row0 * pa.D;
+                    m.sm_dst = jb.sign_mant + e0;
+                    m.code_dst = jb.codes + e0 * N / 8;
+                    m.esc_dst = pa.esc_scratch + tile * pa.tile_elems + (int64_t)row0 * pa.D;
                     m.unit_count = pa.unit_counts + tile * upt + u;
-                    m.tile_count = a.tile_counts + tile;
+                    m.tile_count = pa.tile_counts + tile;
                     m.elems = elems;
                     m.first_unit_of_tile = (u == 0);
                     m.last_unit_of_tile = (u == upt - 1);
+                    m.job = j;
                     mbar_arrive_expect_tx(&s.full[stg], (uint32_t)elems * 2u);
                 }
                 __syncwarp();
-                const uint16_t *usrc = tsrc + (int64_t)row0 * a.ss;
+                const uint16_t *usrc = tsrc + (int64_t)row0 * jb.ss;
                 if (rows_contig) {
                     if (lane == 0) bulk_load(st.in, usrc, (uint32_t)elems * 2u, &s.full[stg]);
                 } else {
                     for (int r = lane; r < rows; r += 32)
-                        bulk_load(st.in + r * a.D, usrc + (int64_t)r * a.ss, (uint32_t)a.D * 2u, &s.full[stg]);
+                        bulk_load(st.in + r * pa.D, usrc + (int64_t)r * jb.ss, (uint32_t)pa.D * 2u, &s.full[stg]);
                 }
             }
         }
+        // do not leave while a copy into this CTA's shared memory may still be in flight (see k_unpack_pipe)
+        if (launch_timed_out(pa.status))
+            for (uint32_t k = it > kStages ? it - kStages : 0; k < it; ++k)
+                mbar_wait(&s.full[k % kStages], (k / kStages) & 1, pa.status, pa.poll_limit);
         return;
     }
 
@@ -857,43 +946,61 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
     for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
     uint32_t it = 0;
     int running = 0;
-    for (int64_t tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+    int cur_job = -1, cur_left = 0;
+    for (int64_t tile = blockIdx.x; tile < pa.n_tiles; tile += gridDim.x) {
         for (int u = 0; u < upt; ++u, ++it) {
             const int stg = it % kStages;
-            if (lane == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status);
+            if (lane == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status, pa.poll_limit);
             __syncwarp();
-            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], a.left, running, cnt2);
+            const int job = s.stage[stg].meta.job;
+            if (job != cur_job) {
+                // Uniform over the CTA (every consumer reads the same sequence of units): hand the finished
+                // job's histogram over and build the new job's code table.  The previous unit ended with
+                // a consumer barrier, so nobody still encodes with the old table.
+                if (HIST && cur_job >= 0) flush_code_counts<N>(cnt2, cur_left, s.hist);
+                consumer_sync();
+                if (HIST && cur_job >= 0 && tid < 256) {
+                    const int hv = s.hist[tid];
+                    if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
+                    s.hist[tid] = 0;
+                }
+                cur_job = job;
+                cur_left = pa.job[job].left;
+                if (tid < 256) {
+                    const uint32_t code = (uint32_t)tid - (uint32_t)cur_left;
+                    s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
+                }
+                consumer_sync();
+            }
+            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], running, cnt2);
+            // the per-thread counters are 16-bit fields and grow by at most 32 per unit
+            if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
         }
     }
-    if (HIST) {
-#pragma unroll
-        for (int v = 1; v < (1 << N); ++v) {
-            const uint32_t mine = (cnt2[v >> 1] >> (16 * (v & 1))) & 0xFFFFu;
-            const uint32_t sum = __reduce_add_sync(kFull, mine);
-            const int bin = a.left + v;
-            if (lane == 0 && sum != 0 && bin >= 0 && bin < 256) atomicAdd(&s.hist[bin], (int)sum);
-        }
+    if (HIST && cur_job >= 0) {
+        flush_code_counts<N>(cnt2, cur_left, s.hist);
         consumer_sync();
         if (tid < 256) {
             const int hv = s.hist[tid];
-            if (hv != 0) atomicAdd(a.hist + tid, hv);
+            if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
         }
     }
     bulk_wait_all();
     __threadfence();
     consumer_sync();
     if (tid == 0) {
-        const unsigned ticket = atomicAdd(a.done, 1u);
+        const unsigned ticket = atomicAdd(pa.done, 1u);
         s.is_last = (ticket == gridDim.x - 1);
     }
     consumer_sync();
     if (!s.is_last) return;
     __threadfence();
-    scan_tile_counts(a, &s.carry, s.scan);
+    scan_tile_counts(pa, &s.carry, s.scan);
 }
 
 // Gather every unit's escape bytes from its scratch slot into the compact per-segment stream.
-// Tile t of segment j starts at seg_off[j] + tile_base[t] - count[t]; its units follow each other.
+// Tile t of global block i starts at blk_off[i] - blk_off[first block of the job] + tile_base[t] -
+// count[t] in its job's stream; its units follow each other.  blockIdx.y is the job.
 // One warp per tile.  All of a tile's metadata is fetched with independent loads (one memory round
 // trip), the bytes move as aligned 32-bit words (the source words are funnel-shifted into the
 // alignment of the destination; only the first and last word of a run use byte stores).
@@ -902,16 +1009,12 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const PackPipeArg
 // four copies of the 256 bins (picked by lane & 3): one copy would serialise most of a warp's
 // shared-memory atomics.
 template <bool HIST>
-__global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__restrict__ scratch,
-                                                             const int32_t *__restrict__ tile_counts,
-                                                             const int32_t *__restrict__ unit_counts,
-                                                             const int32_t *__restrict__ tile_base,
-                                                             const int64_t *__restrict__ seg_off, int64_t n_tiles,
-                                                             int BH, int tile_elems, int unit_elems, int upt,
-                                                             uint8_t *__restrict__ escapes, int64_t capacity,
-                                                             int32_t *__restrict__ hist, int32_t *status) {
+__global__ void __launch_bounds__(kThreads) k_compact_units(const __grid_constant__ PackPipeArgs pa) {
     __shared__ int s_hist[HIST ? kWarps : 1][HIST ? 4 : 1][HIST ? 256 : 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const PackJob &jb = pa.job[blockIdx.y];
+    int32_t *hist = jb.hist;
+    const bool do_hist = HIST && hist != nullptr;
     if (HIST) {
         for (int i = tid; i < kWarps * 4 * 256; i += kThreads) (&s_hist[0][0][0])[i] = 0;
         __syncthreads();
@@ -919,21 +1022,27 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
     int *my_hist = &s_hist[HIST ? warp : 0][HIST ? (lane & 3) : 0][0];
     const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t n_warps = (int64_t)gridDim.x * kWarps;
-    for (int64_t t = warp_global; t < n_tiles; t += n_warps) {
+    const int64_t job_tiles = (int64_t)jb.n_blocks * pa.BH;
+    const int upt = pa.units_per_tile;
+    const int unit_elems = pa.unit_rows * pa.D;
+    const int64_t job_off = __ldg(pa.blk_off + jb.blk0);
+    for (int64_t lt = warp_global; lt < job_tiles; lt += n_warps) {
+        const int64_t t = jb.tile0 + lt;
         // independent loads: one round trip
-        const int c = __ldg(tile_counts + t);
-        const int tb = __ldg(tile_base + t);
-        const int64_t so = __ldg(seg_off + t / BH);
-        int cu = __ldg(unit_counts + t * upt);
+        const int c = __ldg(pa.tile_counts + t);
+        const int tb = __ldg(jb.tile_base + lt);
+        const int64_t so = __ldg(pa.blk_off + t / pa.BH) - job_off;
+        int cu = __ldg(pa.unit_counts + t * upt);
         if (c == 0) continue;
         int64_t dst = so + tb - c;
-        const bool fits = dst >= 0 && dst + c <= capacity;
-        if (!fits && lane == 0) atomicOr(status, ADACODE_STATUS_ESCAPE_OVERFLOW);
+        const bool fits = dst >= 0 && dst + c <= jb.capacity;
+        if (!fits && lane == 0) atomicOr(pa.status, ADACODE_STATUS_ESCAPE_OVERFLOW);
         for (int u = 0; u < upt; ++u) {
-            if (u > 0) cu = __ldg(unit_counts + t * upt + u);
+            if (u > 0) cu = __ldg(pa.unit_counts + t * upt + u);
             // unit slots start on 16-byte boundaries
-            const uint32_t *src4 = reinterpret_cast<const uint32_t *>(scratch + t * tile_elems + (int64_t)u * unit_elems);
-            uint8_t *d8 = escapes + dst;
+            const uint32_t *src4 =
+                reinterpret_cast<const uint32_t *>(pa.esc_scratch + t * pa.tile_elems + (int64_t)u * unit_elems);
+            uint8_t *d8 = jb.escapes + dst;
             const int r = (int)((uintptr_t)d8 & 3);
             uint32_t *dst32 = reinterpret_cast<uint32_t *>(d8 - r);
             const int n_words = (r + cu + 3) >> 2;             // destination words touched
@@ -961,7 +1070,7 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
                                     reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
                         }
                     }
-                    if (HIST) {
+                    if (do_hist) {
                         // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
                         uint32_t x = w[k + 1];
 #pragma unroll
@@ -975,7 +1084,7 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const uint8_t *__res
             dst += cu;
         }
     }
-    if (HIST) {
+    if (do_hist) {
         __syncthreads();
         int total = 0;
 #pragma unroll

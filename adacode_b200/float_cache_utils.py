@@ -584,11 +584,18 @@ class float11Layer(DynamicLayer):
         prefix = self._compressed_prefix_seq_len
         total = prefix + res_len
         outs = []
-        for which, segs, res in (('k', self._key_segments, res_k), ('v', self._value_segments, res_v)):
+        if self.dense_workspace == 'shared':
+            # keys and values are decoded by one launch when they have one shape
+            todo = []
+            for which, segs in (('k', self._key_segments), ('v', self._value_segments)):
+                B, H, _, D = segs[0].original_shape
+                dense = self._workspace.view(self.cache_device, which, (B, H, total, D))
+                todo.append((segs, dense, self._segment_table(which, segs)))
+            codec.unpack_segments_multi(todo)
+        for i, (which, segs, res) in enumerate((('k', self._key_segments, res_k), ('v', self._value_segments, res_v))):
             B, H, _, D = segs[0].original_shape
             if self.dense_workspace == 'shared':
-                dense = self._workspace.view(self.cache_device, which, (B, H, total, D))
-                codec.unpack_segments(segs, dense, table=self._segment_table(which, segs))
+                dense = todo[i][1]
             else:
                 # per-layer mirror: lossless packing never changes a token's bits, so whatever was
                 # written once stays valid; only blocks not yet present are decoded

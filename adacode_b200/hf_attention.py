@@ -13,10 +13,12 @@ the dense tensors, as before.
     with fused_decode(cache):
         out = model.generate(ids, past_key_values=cache, ...)
 
-Limits: every cached token is attended to (no padding mask, no sliding window), head_dim 64 or
-128.  Results are close to, not bit-identical with, the
-materialising path (different summation order), so generated tokens can differ where two
-logits are nearly tied.
+Limits: every cached token is attended to, head_dim 64 or 128.  A step whose attention mask hides
+any cached position (left-padded batches) or whose layer uses a sliding window cannot be served by
+the kernel; such a step raises instead of attending to the wrong tokens, and ``fused_decode``
+refuses a model whose attention implementation is not the one registered here (its SDPA would see
+one token only).  Results are close to, not bit-identical with, the materialising path
+(different summation order), so generated tokens can differ where two logits are nearly tied.
 """
 from __future__ import annotations
 
@@ -35,11 +37,27 @@ def float11_fused_attention(module, query, key, value, attention_mask, dropout: 
     cache = _active_cache
     if cache is not None and query.shape[2] == 1 and getattr(cache, '_fused_decode', False):
         layer = cache.layers[module.layer_idx]
+        if getattr(module, 'sliding_window', None):
+            raise NotImplementedError('float11_fused attention has no sliding window; use the materialising path')
+        if attention_mask is not None and not _mask_shows_everything(cache, attention_mask):
+            raise NotImplementedError('float11_fused attention attends to every cached token, but this step\'s '
+                                      'attention mask hides some (left padding?); use the materialising path')
         out = layer.decode_attention(query, scale=scaling)           # [B, Hq, 1, D]
         return out.transpose(1, 2).contiguous(), None               # [B, 1, Hq, D]
     from transformers.integrations.sdpa_attention import sdpa_attention_forward
     return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling,
                                   **kwargs)
+
+
+def _mask_shows_everything(cache, mask: torch.Tensor) -> bool:
+    """True when a boolean mask is all True or an additive mask is all zero.  All layers of a
+    forward pass get the same mask object, so the (synchronising) check runs once per step."""
+    seen = getattr(cache, '_fused_mask_seen', None)
+    if seen is not None and seen[0] is mask:
+        return seen[1]
+    ok = bool(mask.all()) if mask.dtype == torch.bool else bool((mask == 0).all())
+    cache._fused_mask_seen = (mask, ok)
+    return ok
 
 
 def register() -> str:
@@ -50,9 +68,17 @@ def register() -> str:
 
 
 @contextlib.contextmanager
-def fused_decode(cache):
-    """Single-token updates of ``cache`` skip the dense rebuild while this context is active."""
+def fused_decode(cache, model=None):
+    """Single-token updates of ``cache`` skip the dense rebuild while this context is active.
+    Pass the model (or its config) to have its attention implementation checked: with any other
+    implementation the model's own attention would run on the one token ``update`` returns."""
     global _active_cache
+    if model is not None:
+        cfg = getattr(model, 'config', model)
+        impl = getattr(cfg, '_attn_implementation', None)
+        if impl != ATTENTION_NAME:
+            raise RuntimeError(f"fused_decode needs config._attn_implementation == '{ATTENTION_NAME}' "
+                               f'(call hf_attention.register() and set it); found {impl!r}')
     previous = _active_cache
     _active_cache = cache
     cache._fused_decode = True
@@ -60,4 +86,5 @@ def fused_decode(cache):
         yield cache
     finally:
         cache._fused_decode = False
+        cache._fused_mask_seen = None
         _active_cache = previous

@@ -74,5 +74,10 @@ def _make_config_class(name: str, hub_path: str, stem: str):
     return type(name, (model_default_config,), {'__init__': __init__, '__doc__': f'Cache settings of {stem}.'})
 
 
+def default_kv_calibration_path(name: str) -> str:
+    """Where ``model_config_map[name]()`` looks for the calibration JSON of that model."""
+    return f'./model_configs/kv_test_{_KV_MODELS[name][1]}_exp.json'
+
+
 model_config_map = {name: _make_config_class(name, *spec) for name, spec in _KV_MODELS.items()}
 globals().update(model_config_map)

@@ -1,27 +1,33 @@
 """Benchmark of the float11 KV-cache hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--blocks main,config1,...]
 
-Workload (BASELINE config 1, "Qwen3-4B-shaped cache"): 36 layers x (K, V) of
-[1, 8, 20480, 128] bf16, per-layer sigma_c ~ LogNormal(mu_l, 1) with mu_l spread over [-1, 1],
-2 % outlier channels x30, a per-channel offset ~ N(0, 2) on K; windows and code lengths
-calibrated from a separately seeded tensor of the same distribution.  One STEP packs the whole
-cache (72 tensors, 160 blocks each, one pack launch per tensor) and unpacks it again.
-With N > 1 every rank owns one such sequence (sequences sharded across GPUs, weak scaling) and
-the per-layer exponent histograms are all-reduced once per step over NCCL, which is the only
-exchange the path has.
+Primary workload at every N (the multi-GPU stress configuration): a Qwen3-8B-shaped cache,
+36 layers x (K, V) of [64, 8, 8192, 128] bf16, the 64 sequences dealt out contiguously to the N
+ranks; sigma doubles for KV heads 4-7 from token 4096 on; 0.1 % of the exponent fields lie
+outside the calibrated window and 0.01 % are zero.  One STEP, per rank and layer, with everything
+resident in HBM: tokens 0-4095 of K and V are packed by one launch with the calibrated windows,
+tokens 4096-8191 by a second launch with the windows the code-length adjuster chose from the
+histogram of that span summed over ALL ranks (NCCL all-reduce, the path's only exchange; it runs on
+a side stream and its result drives the next step's windows), and after all layers are packed
+every layer's 64 segments per tensor (two windows) are unpacked again through segment tables.
 
-Reported, in one JSON line on rank 0:
-  value     BF16-equivalent GB/s of the round trip with everything resident in HBM:
-            (bytes of bf16 packed + bytes of bf16 unpacked) / device time, summed over ranks
-  e2e       the same through the public API (Float11Cache.update / materialize_layer) with K/V
-            coming from pinned host memory and the unpacked tensors copied back to the host
-  roofline  the pack kernel (the slower of the two) against the measured HBM copy bandwidth
-  cpu_baseline  the CPU restatement of the reference's pack/unpack on the host cores
+Reported in one JSON line on rank 0:
+  value         BF16-equivalent GB/s of that round trip, summed over ranks (max time over ranks)
+  roofline      the pack kernels against the measured HBM copy bandwidth; roofline_unpack likewise
+  e2e           the same metric through Float11Cache.update + materialize_layer with K/V in pinned
+                host memory and the unpacked tensors copied back, copies inside the timed region
+  parity        bit-exact round trip of every tensor at full size; byte parity of a reduced
+                replica run through Float11Cache(hist_reduce=NCCL all-reduce) against the CPU
+                oracle's unsharded pack
+  cpu_baseline  the CPU restatement of the reference's pack/unpack on a bounded sample (N = 1 only)
+With N = 1 further blocks cover the other benchmark configurations (config1: Qwen3-4B-shaped
+prefill + 128 decode appends, config3: MLA latent cache, config2: Llama-3.1-8B-shaped generation).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -33,49 +39,91 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-LAYERS, KV_HEADS, PROMPT, HEAD_DIM, BLOCK = 36, 8, 20480, 128, 128
-WORKLOAD = 'config1: Qwen3-4B-shaped cache, 36 layers x K,V [1,8,20480,128] bf16, prefill packed once then unpacked'
 METRIC = 'kv_pack_unpack_bf16_equiv_GBps'
-# DRAM bytes per element of one pack launch (k_pack_pipe + k_compact_units, dram read + write),
-# from the ncu capture summarised in profiles/pipelined_k_pack_pipe_k_unpack_pipe_16x8x8192x128_nbits3.md;
-# scaled to a bench launch by its element count (streaming kernels: traffic is proportional to elements).
+BLOCK = 128
+# stress configuration (primary workload)
+S4_LAYERS, S4_BATCH, S4_HEADS, S4_SEQ, S4_DIM, S4_SHIFT = 36, 64, 8, 8192, 128, 4096
+S4_SHIFT_HEADS = (4, 5, 6, 7)
+S4_P_WINDOW, S4_P_ZERO = 1e-3, 1e-4
+# Qwen3-4B-shaped configuration
+C1_LAYERS, C1_HEADS, C1_PROMPT, C1_DIM, C1_DECODE = 36, 8, 20480, 128, 128
+# DRAM bytes per element of one pack launch (k_pack_pipe + k_compact_units, dram read + write) from the
+# ncu capture of a smaller launch of the same kernels; traffic is proportional to elements for these
+# streaming kernels, so it is scaled to a bench launch by its element count.
 PACK_DRAM_BYTES_PER_ELEM = 3.19
 
 
-def synth_layer(layer: int, device, seed: int, which: str):
-    """One layer's K or V, generated on `device` from a seeded generator."""
-    import torch
-    g = torch.Generator(device=device).manual_seed(1000 * seed + 2 * layer + (which == 'v'))
-    mu = -1.0 + 2.0 * layer / (LAYERS - 1)
-    sigma = torch.exp(mu + torch.randn(KV_HEADS, HEAD_DIM, generator=g, device=device))
-    sigma = torch.where(torch.rand(KV_HEADS, HEAD_DIM, generator=g, device=device) < 0.02, sigma * 30.0, sigma)
-    x = torch.randn(1, KV_HEADS, PROMPT, HEAD_DIM, generator=g, device=device) * sigma[None, :, None, :]
-    if which == 'k':
-        x = x + (2.0 * torch.randn(KV_HEADS, HEAD_DIM, generator=g, device=device))[None, :, None, :]
-    return x.to(torch.bfloat16)
+class StubConfig:
+    """What the cache classes read from a model config."""
+
+    def __init__(self, num_hidden_layers: int, **extra):
+        self.num_hidden_layers = num_hidden_layers
+        for k, v in extra.items():
+            setattr(self, k, v)
+
+    def get_text_config(self, decoder: bool = True):
+        return self
 
 
-def calibrate(device):
-    """(right, nbits) per layer and tensor from seed-1 tensors, by the calibration rule; code
-    lengths above 4 (which the tiled cache rejects) fall back to the run-time adjuster's rule."""
-    import torch
-    from adacode_b200 import best_bit_analysis_kv_cache as calib
-    from adacode_b200 import codec
-    rights, nbits = [], []
-    for l in range(LAYERS):
-        pr, pn = [], []
+def workload_config(world: int) -> dict:
+    """The `config` object of the JSON line; the reference arm prints the same one."""
+    return {
+        'workload': ('config4: Qwen3-8B-shaped cache, 36 layers x K,V [64,8,8192,128] bf16 sharded by sequence; '
+                     'sigma x2 for heads 4-7 from token 4096; 0.1% out-of-window and 0.01% zero exponents; '
+                     'per layer: pack tokens 0-4095, pack tokens 4096-8191 with adjuster-chosen windows, unpack all'),
+        'sequences_per_gpu': S4_BATCH // world, 'block_size': BLOCK,
+        'l2': 'per-rank working set of a step (inputs + planes) exceeds L2 many times over; all layers are packed '
+              'before any is unpacked, so nothing is re-read from L2',
+        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs)',
+    }
+
+
+# --------------------------------------------------------------------------------------
+# synthetic data and calibration (shared by both arms: identical bytes on CPU and GPU)
+# --------------------------------------------------------------------------------------
+
+def s4_tables(layer: int, which: str):
+    import kv_synth
+    return kv_synth.channel_tables(S4_HEADS, S4_DIM, seed=4000 + 2 * layer + (which == 'v'), key_offset=(which == 'k'))
+
+
+def s4_stream(layer: int, which: str, seed: int = 0) -> int:
+    return 100000 * seed + 2 * layer + (which == 'v')
+
+
+def s4_slab(layer: int, which: str, b0: int, nb: int, s0: int, ns: int, device, window=None, seed: int = 0):
+    """Sequences b0..b0+nb, tokens s0..s0+ns of one tensor of the stress configuration.  `window` =
+    (right, nbits) adds the injected escapes relative to that window."""
+    import kv_synth
+    sigma, offset = s4_tables(layer, which)
+    esc = None
+    if window is not None:
+        right, nbits = window
+        esc = (right - 2 ** nbits + 1, right, S4_P_WINDOW, S4_P_ZERO)
+    return kv_synth.kv_tensor(s4_stream(layer, which, seed), (nb, S4_HEADS, ns, S4_DIM), sigma, offset, device,
+                              b0=b0, s0=s0, shift_from=S4_SHIFT, shift_heads=S4_SHIFT_HEADS, escapes=esc)
+
+
+def calibrate_from(hist) -> tuple:
+    """(right, nbits) by the offline calibration rule; code lengths above 4 (which the tiled cache
+    rejects) fall back to the run-time adjuster's rule."""
+    from oracle import float11_oracle as O
+    r, n = O.calibrate_coo(hist)
+    if n > 4:
+        r, n = O.choose_params(hist)
+    return int(r), int(n)
+
+
+def s4_calibration(layers) -> dict:
+    """Windows per (layer, 'k'/'v') from a separately seeded tensor of the unshifted distribution
+    ([1, 8, 1024, 128], CPU; cheap enough for both arms)."""
+    from oracle import float11_oracle as O
+    out = {}
+    for l in layers:
         for which in ('k', 'v'):
-            x = synth_layer(l, device, 1, which)[:, :, :2048]
-            hist = codec.exponent_hist(x).cpu().tolist()
-            r, n = calib.analysis_best_bits_coo([hist])
-            r, n = r[0], n[0]
-            if n > 4:
-                r, n = codec.analysis_best_bits(hist)
-            pr.append(r)
-            pn.append(n)
-        rights.append(tuple(pr))
-        nbits.append(tuple(pn))
-    return rights, nbits
+            x = s4_slab(l, which, 0, 1, 0, 1024, 'cpu', seed=1)
+            out[(l, which)] = calibrate_from(O.exponent_hist(x))
+    return out
 
 
 class ClockSampler:
@@ -144,27 +192,50 @@ def measured_hbm_peak():
 # CPU arm: the restatement of the reference's pack/unpack on the host cores
 # --------------------------------------------------------------------------------------
 
-def cpu_round_trip(blocks_per_tensor: int, tensors: int, right=130, nbits=3, seed=0, repeats=1):
-    """Pack and unpack `tensors` tensors of `blocks_per_tensor` 128-token blocks of [1, 8, 128, 128]
-    with the OpenMP oracle, all blocks of a tensor in one call (handed over as a batch of blocks
-    so that every host thread has tiles to work on).  Returns (seconds, elements, threads)."""
+CPU_SAMPLE_LAYERS, CPU_SAMPLE_SEQS = 2, 2
+CPU_SAMPLE_TEXT = (f'layers 0-{CPU_SAMPLE_LAYERS - 1}, sequences 0-{CPU_SAMPLE_SEQS - 1} of the workload: K and V '
+                   f'[{CPU_SAMPLE_SEQS},8,8192,128] per layer, the same bytes and windows as the GPU arm '
+                   '(tokens 0-4095 calibrated window, 4096-8191 the window the adjuster rule picks from that span\'s histogram), '
+                   'every 128-token block packed and unpacked by the OpenMP oracle')
+
+
+def cpu_sample():
+    """The CPU arm's inputs: [(uint16 array [n_blocks, b*8... ] per span, right, nbits)], built once."""
+    import numpy as np
+    from oracle import float11_oracle as O
+    calib = s4_calibration(range(CPU_SAMPLE_LAYERS))
+    spans = []
+    for l in range(CPU_SAMPLE_LAYERS):
+        for which in ('k', 'v'):
+            win = calib[(l, which)]
+            x = s4_slab(l, which, 0, CPU_SAMPLE_SEQS, 0, S4_SEQ, 'cpu', window=win)
+            u = O.as_u16(x)
+            # blocks as a batch of tiles: [n_blocks * b, 8, 128, 128] keeps every host thread busy
+            def blocks_of(part):
+                b, h, s, d = part.shape
+                return np.ascontiguousarray(part.reshape(b, h, s // BLOCK, BLOCK, d).transpose(2, 0, 1, 3, 4)
+                                            .reshape((s // BLOCK) * b, h, BLOCK, d))
+            a, bpart = u[:, :, :S4_SHIFT], u[:, :, S4_SHIFT:]
+            win_b = O.choose_params(O.exponent_hist(bpart))
+            spans.append((blocks_of(a), win[0], win[1]))
+            spans.append((blocks_of(bpart), win_b[0], win_b[1]))
+    return spans
+
+
+def cpu_round_trip(spans, repeats: int = 1):
+    """Pack and unpack every span with the OpenMP oracle on all host cores we may run on.
+    Returns (seconds, elements, threads)."""
     import numpy as np
     from oracle import float11_oracle as O
     try:
         O.set_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1; use every core we may run on
     except AttributeError:
         O.set_threads(os.cpu_count() or 1)
-    rng = np.random.default_rng(seed)
-    sigma = np.exp(rng.standard_normal((KV_HEADS, 1, HEAD_DIM))).astype(np.float32)
-    data = []
-    for t in range(tensors):
-        base = rng.standard_normal((blocks_per_tensor, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.float32) * sigma
-        data.append((base.view(np.uint32) >> 16).astype(np.uint16))     # bf16 by truncation
-    O.pack_block(data[0][:1], right, nbits)                             # load the library, warm the threads
+    O.pack_block(spans[0][0][:1], spans[0][1], spans[0][2])             # load the library, warm the threads
     t0 = time.perf_counter()
     n = 0
     for _ in range(repeats):
-        for x in data:
+        for x, right, nbits in spans:
             p = O.pack_block(x, right, nbits, need_hist=True)
             y = O.unpack_block(p)
             n += x.size
@@ -174,28 +245,28 @@ def cpu_round_trip(blocks_per_tensor: int, tensors: int, right=130, nbits=3, see
 
 
 def run_reference_arm(args) -> None:
-    """The reference has no compiled code and its Python sources do not travel to the GPU box;
-    this arm times the CPU restatement of its pack/unpack (the oracle, pinned byte for byte to the
-    reference's own pack) on all host cores, on a bounded sample of the same workload."""
+    """The reference has no compiled code and its Python sources do not travel to the GPU box; this arm
+    times the CPU restatement of its pack/unpack (the oracle, pinned byte for byte to the reference's
+    own pack) on all host cores, on a bounded sample of the same workload."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    blocks = PROMPT // BLOCK
-    times, n = [], 0
+    world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
+    spans = cpu_sample()
+    times, n, threads = [], 0, 1
     for i in range(args.warmup + args.steps):
-        dt, n, threads = cpu_round_trip(blocks, 2, seed=i, repeats=LAYERS)   # K and V of every layer
+        dt, n, threads = cpu_round_trip(spans)
         if i >= args.warmup:
             times.append(dt)
     t = sum(times) / len(times)
     value = 2 * 2 * n / t / 1e9
-    sample = (f'whole workload per step: {LAYERS} layers x K,V [1,8,20480,128] packed and unpacked '
-              '(one layer\'s random data reused for every layer)')
     line = {
-        'impl': 'reference', 'metric': METRIC, 'value': round(value, 3), 'unit': 'GB/s', 'n_gpus': args.gpus,
+        'impl': 'reference', 'metric': METRIC, 'value': round(value, 3), 'unit': 'GB/s', 'n_gpus': world,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(t * 1e3, 3), 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
-        'config': {'workload': WORKLOAD, 'sample': sample},
-        'cpu_baseline': {'value': round(value, 3), 'unit': 'GB/s', 'cores': threads, 'kind': 'port', 'sample': sample},
+        'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
+        'config': workload_config(world),
+        'cpu_baseline': {'value': round(value, 3), 'unit': 'GB/s', 'cores': threads, 'kind': 'port',
+                         'sample': CPU_SAMPLE_TEXT},
         'e2e': {'value': round(value, 3), 'unit': 'GB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
@@ -203,31 +274,51 @@ def run_reference_arm(args) -> None:
 
 
 # --------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm, primary workload
 # --------------------------------------------------------------------------------------
 
-class PackedTensorSlots:
-    """Preallocated outputs of one tensor's pack launch (raw C-ABI use: no allocation and no
-    host read inside the timed region)."""
+class SpanSlots:
+    """Preallocated outputs of one span (n_blocks 128-token blocks) of one tensor: raw C-ABI use, no
+    allocation and no host read inside the timed region.  Planes are sized for 4-bit codes so that
+    the adjuster may move the span to any code length."""
 
-    def __init__(self, x, right, nbits, device):
+    def __init__(self, x, right, nbits, device, margin: float = 1.5, offsets=None):
         import torch
         from adacode_b200 import codec
         self.x, self.right, self.nbits = x, int(right), int(nbits)
-        self.left = self.right - 2 ** self.nbits + 1
+        B, H, S, D = x.shape
+        self.n_blocks = S // BLOCK
+        n = x.numel()
         chunk, _ = codec.pack_blocks(x, right, nbits, BLOCK)            # sizing pass (also a warm-up)
-        self.n_blocks = chunk.n_blocks
         self.n_escapes = chunk.n_escapes
-        self.sign_mant, self.codes, self.tile_base = chunk.sign_mant, chunk.codes, chunk.tile_base
-        self.escapes = torch.empty(max(self.n_escapes, 16), dtype=torch.uint8, device=device)
-        self.meta = torch.zeros(self.n_blocks + 2, dtype=torch.int64, device=device)
+        del chunk
+        self.sign_mant = torch.empty(n, dtype=torch.uint8, device=device)
+        self.codes = torch.empty(n // 2, dtype=torch.uint8, device=device)
+        self.tile_base = torch.empty(B * H * self.n_blocks, dtype=torch.int32, device=device)
+        self.cap = int(max(self.n_escapes * margin, n // 16)) + 4096
+        self.escapes = torch.empty(self.cap, dtype=torch.uint8, device=device)
+        self.offsets = offsets if offsets is not None else torch.zeros(self.n_blocks + 1, dtype=torch.int64, device=device)
+
+    @property
+    def left(self):
+        return self.right - 2 ** self.nbits + 1
+
+
+def fill_pack_job(jb, s: 'SpanSlots', hist_ptr: int) -> None:
+    sb, sh, ss, _ = s.x.stride()
+    jb.src_bf16, jb.stride_b, jb.stride_h, jb.stride_s = s.x.data_ptr(), sb, sh, ss
+    jb.n_blocks, jb.right = s.n_blocks, s.right
+    jb.sign_mant, jb.codes, jb.escapes = s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr()
+    jb.escapes_capacity = s.cap
+    jb.tile_base, jb.seg_escape_offsets = s.tile_base.data_ptr(), s.offsets.data_ptr()
+    jb.hist256 = hist_ptr
 
 
 def run_gpu_arm(args) -> None:
+    import numpy as np
     import torch
     import torch.distributed as dist
-    from adacode_b200 import Float11Cache, _lib, codec
-    from tests.scenarios import StubConfig
+    from adacode_b200 import _lib, codec
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -236,121 +327,465 @@ def run_gpu_arm(args) -> None:
     dev = torch.device('cuda', local_rank)
     if world > 1:
         dist.init_process_group('nccl', device_id=dev)
+    blocks = set((args.blocks or ('all' if world == 1 else 'main')).split(','))
+    if 'all' in blocks:
+        blocks = {'main', 'config1', 'config3', 'config2'}
+    line = {}
+    if 'main' in blocks:
+        line = stress_workload(args, dev, world, rank, local_rank)
+    extras = {}
+    if rank == 0 and world == 1:
+        for name, fn in (('config1', config1_block), ('config3', config3_block), ('config2', config2_block)):
+            if name in blocks:
+                torch.cuda.empty_cache()
+                try:
+                    extras[name] = fn(args, dev)
+                except Exception as exc:      # an extra block must not take the headline down with it
+                    extras[name] = {'error': f'{type(exc).__name__}: {exc}'[:300]}
+    if rank == 0:
+        line.update(extras)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from adacode_b200 import _lib, codec
+    from oracle import float11_oracle as O
+
     L = _lib.lib()
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    main = torch.cuda.current_stream(dev)
+    stream = main.cuda_stream
+    per = S4_BATCH // world
+    b0 = rank * per
+    layers = list(range(args.layers or S4_LAYERS))
+    calib = s4_calibration(layers)
+    half = S4_SHIFT
 
-    rights, nbits = calibrate(dev)
-    slots = []
-    for l in range(LAYERS):
+    # ---- inputs and preallocated outputs -------------------------------------------------
+    n_layers = len(layers)
+    nseg = S4_SEQ // BLOCK
+    nb_span = half // BLOCK
+    # segment escape offsets of every span in one tensor [layer][k/v][span][blocks + 1]
+    offsets_all = torch.zeros((n_layers, 2, 2, nb_span + 1), dtype=torch.int64, device=dev)
+    esc_base = torch.zeros((n_layers, 2, 2, 1), dtype=torch.int64)
+    slots = []                      # per layer: {'a': (K span A, V span A), 'b': (K span B, V span B)}
+    for li, l in enumerate(layers):
+        ent = {'a': [], 'b': []}
         for wi, which in enumerate(('k', 'v')):
-            x = synth_layer(l, dev, 7 * rank, which)
-            slots.append(PackedTensorSlots(x, rights[l][wi], nbits[l][wi], dev))
-    n_elems = sum(s.x.numel() for s in slots)
-    n_esc = sum(s.n_escapes for s in slots)
-    code_bytes = sum(s.x.numel() * s.nbits // 8 for s in slots)
-    tiles = 1 * KV_HEADS * (PROMPT // BLOCK)
-    ws = codec._scratch_for(dev).workspace_for(tiles, BLOCK * HEAD_DIM)
-    hists = torch.zeros((LAYERS * 2, 256), dtype=torch.int32, device=dev)
-    status = codec._scratch_for(dev).status
-    out = [torch.empty((1, KV_HEADS, PROMPT, HEAD_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    sb, sh, ss, _ = slots[0].x.stride()
-    db, dh, ds, _ = out[0].stride()
-
-    # K and V of a layer are independent: they are packed (and unpacked) on two streams, each with
-    # its own pack scratch, so that the tail of one launch overlaps the head of the other
+            win = calib[(l, which)]
+            x = s4_slab(l, which, b0, per, 0, S4_SEQ, dev, window=win)
+            ent['a'].append(SpanSlots(x[:, :, :half], win[0], win[1], dev, offsets=offsets_all[li, wi, 0]))
+            ent['b'].append(SpanSlots(x[:, :, half:], win[0], win[1], dev, margin=2.0, offsets=offsets_all[li, wi, 1]))
+            ent.setdefault('x', []).append(x)
+            esc_base[li, wi, 0, 0] = ent['a'][wi].escapes.data_ptr()
+            esc_base[li, wi, 1, 0] = ent['b'][wi].escapes.data_ptr()
+        slots.append(ent)
+    esc_base = esc_base.to(dev)
+    n_elems = sum(x.numel() for ent in slots for x in ent['x'])
+    tiles_per_launch = 2 * per * S4_HEADS * (half // BLOCK)
+    ws = torch.zeros(L.adacode_pack_workspace_bytes(tiles_per_launch, BLOCK * S4_DIM), dtype=torch.uint8, device=dev)
+    hists = torch.zeros((n_layers, 2, 2, 256), dtype=torch.int32, device=dev)       # [layer][span][k/v]
+    hists_red = torch.zeros((n_layers, 2, 256), dtype=torch.int32, device=dev)      # span B, summed over ranks
+    params_dev = torch.zeros((n_layers * 2, 2), dtype=torch.int32, device=dev)
+    params_host = torch.zeros((n_layers * 2, 2), dtype=torch.int32).pin_memory()
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    out = [torch.empty((per, S4_HEADS, S4_SEQ, S4_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     side = torch.cuda.Stream(dev)
-    streams = (stream, side.cuda_stream)
-    ws2 = torch.zeros_like(ws)
-    scratch = (ws, ws2)
-    fork, join = torch.cuda.Event(), torch.cuda.Event()
+    ev_packed, ev_params = torch.cuda.Event(), torch.cuda.Event()
+    rec_dtype = codec._segment_dtype()
+    tables_host = np.zeros((n_layers, 2, nseg), dtype=rec_dtype)
+    tables_dev = torch.zeros((n_layers, 2, nseg * rec_dtype.itemsize), dtype=torch.uint8, device=dev)
+    tables_dirty = [True] * n_layers
+    launches = {'pack': 0, 'unpack': 0}
 
-    def on_two_streams(fn):
-        main = torch.cuda.current_stream(dev)
-        fork.record(main)
-        side.wait_event(fork)
-        fn()
-        join.record(side)
-        main.wait_event(join)
+    def pack_layer(li: int) -> None:
+        ent = slots[li]
+        for si, span in enumerate(('a', 'b')):
+            pair = ent[span]
+            groups = [pair] if pair[0].nbits == pair[1].nbits else [[pair[0]], [pair[1]]]
+            for grp in groups:
+                jobs = (_lib.PackJob * len(grp))()
+                for jb, s in zip(jobs, grp):
+                    fill_pack_job(jb, s, hists[li, si, pair.index(s)].data_ptr())
+                rc = L.adacode_pack_jobs(ctypes.addressof(jobs), len(grp), per, S4_HEADS, BLOCK, S4_DIM, grp[0].nbits,
+                                         ws.data_ptr(), ws.numel(), status.data_ptr(), stream)
+                if rc:
+                    _lib.check(rc, 'adacode_pack_jobs')
+                launches['pack'] += 2          # k_pack_pipe + k_compact_units
 
-    def pack_all():
-        for i, s in enumerate(slots):
-            w = scratch[i & 1]
-            rc = L.adacode_pack_tiles(s.x.data_ptr(), sb, sh, ss, 1, KV_HEADS, s.n_blocks, BLOCK, HEAD_DIM, s.right,
-                                      s.nbits, s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr(),
-                                      s.escapes.numel(), s.tile_base.data_ptr(), s.meta.data_ptr(),
-                                      hists[i].data_ptr(), w.data_ptr(), w.numel(),
-                                      s.meta.data_ptr() + 8 * (s.n_blocks + 1), streams[i & 1])
-            if rc:
-                _lib.check(rc, 'adacode_pack_tiles')
+    def refresh_table(li: int) -> None:
+        """Segment records of layer li (64 per tensor: span A then span B).  Escape streams start at
+        offsets only the device knows, so every record names its span's whole stream; the unpack
+        kernel adds the block's offset itself when given the span's offset array -- which the table
+        form does not carry.  So the records are completed on the device: see complete_tables()."""
+        ent = slots[li]
+        for wi in range(2):
+            rows = tables_host[li, wi]
+            for si, span in enumerate(('a', 'b')):
+                s = ent[span][wi]
+                js = np.arange(s.n_blocks, dtype=np.int64)
+                part = rows[si * s.n_blocks:(si + 1) * s.n_blocks]
+                bh_tile = per * S4_HEADS * BLOCK * S4_DIM
+                part['sign_mant'] = s.sign_mant.data_ptr() + js * bh_tile
+                part['codes'] = s.codes.data_ptr() + js * (bh_tile * s.nbits // 8)
+                part['escapes'] = s.escapes.data_ptr()
+                part['tile_base'] = s.tile_base.data_ptr() + js * (4 * per * S4_HEADS)
+                part['escapes_len'] = 0
+                part['dst_seq_offset'] = (si * s.n_blocks + js) * BLOCK
+                part['left'] = s.left
+                part['nbits'] = s.nbits
+        tables_dev[li].copy_(torch.from_numpy(tables_host[li].view(np.uint8).reshape(2, -1)), non_blocking=False)
+        tables_dirty[li] = False
 
-    def unpack_all():
-        for i, s in enumerate(slots):
-            rc = L.adacode_unpack_tiles(s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr(),
-                                        s.escapes.numel(), s.tile_base.data_ptr(), s.meta.data_ptr(), 1, KV_HEADS,
-                                        s.n_blocks, BLOCK, HEAD_DIM, s.left, s.nbits, out[i & 1].data_ptr(), db, dh, ds,
-                                        status.data_ptr(), streams[i & 1])
-            if rc:
-                _lib.check(rc, 'adacode_unpack_tiles')
+    def complete_tables() -> None:
+        """escapes = span stream + seg_offsets[j], escapes_len = seg_offsets[j + 1] - seg_offsets[j] for all
+        records at once, on the device (the offsets change whenever a window changes)."""
+        words = rec_dtype.itemsize // 8
+        t64 = tables_dev.view(torch.int64).view(n_layers, 2, 2, nb_span, words)
+        t64[..., 2] = esc_base + offsets_all[..., :-1]
+        t64[..., 4] = offsets_all[..., 1:] - offsets_all[..., :-1]
 
-    def step(ev=None):
+    def unpack_layer(li: int) -> None:
+        jobs = (_lib.UnpackJob * 2)()
+        for wi in range(2):
+            db, dh, ds, _ = out[wi].stride()
+            jobs[wi].segments_dev, jobs[wi].n_segments = tables_dev[li, wi].data_ptr(), nseg
+            jobs[wi].dst_bf16 = out[wi].data_ptr()
+            jobs[wi].dstride_b, jobs[wi].dstride_h, jobs[wi].dstride_s = db, dh, ds
+        rc = L.adacode_unpack_jobs(ctypes.addressof(jobs), 2, per, S4_HEADS, BLOCK, S4_DIM, status.data_ptr(), stream)
+        if rc:
+            _lib.check(rc, 'adacode_unpack_jobs')
+        launches['unpack'] += 1
+
+    adopted = {'changes': 0}
+
+    def adopt_params() -> None:
+        """Windows of span B from the previous step's all-reduced histograms (already on the host)."""
+        ev_params.synchronize()
+        p = params_host.view(n_layers, 2, 2).tolist()
+        for li in range(n_layers):
+            for wi in range(2):
+                r, n = p[li][wi]
+                s = slots[li]['b'][wi]
+                if n >= 1 and (r, n) != (s.right, s.nbits):
+                    s.right, s.nbits = int(r), int(n)
+                    tables_dirty[li] = True
+                    adopted['changes'] += 1
+
+    first = {'done': False}
+
+    def step(ev=None, check=None):
+        if first['done']:
+            adopt_params()
+        for li in range(n_layers):
+            if tables_dirty[li]:
+                refresh_table(li)
         hists.zero_()
         if ev:
-            ev[0].record()
-        on_two_streams(pack_all)
+            ev[0].record(main)
+        for li in range(n_layers):
+            pack_layer(li)
         if ev:
-            ev[1].record()
-        if world > 1:
-            dist.all_reduce(hists)          # every shard sees the histogram of the whole batch
-        on_two_streams(unpack_all)
+            ev[1].record(main)
+        # the adjuster's exchange: span-B histograms summed over all ranks, then the device-side
+        # chooser; on a side stream, because the unpack below does not depend on it
+        ev_packed.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ev_packed)
+            hists_red.copy_(hists[:, 1])
+            if world > 1:
+                dist.all_reduce(hists_red)
+            rc = L.adacode_choose_params(hists_red.data_ptr(), n_layers * 2, params_dev.data_ptr(), side.cuda_stream)
+            if rc:
+                _lib.check(rc, 'adacode_choose_params')
+            params_host.copy_(params_dev, non_blocking=True)
+            ev_params.record(side)
+        first['done'] = True
+        complete_tables()
         if ev:
-            ev[2].record()
+            ev[2].record(main)
+        for li in range(n_layers):
+            unpack_layer(li)
+            if check is not None:
+                check(li)
+        if ev:
+            ev[3].record(main)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     barrier()
+    launches['pack'] = launches['unpack'] = 0
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    t_begin.record()
+    t_begin.record(main)
     for k in range(args.steps):
         step(evs[k])
-    t_end.record()
+    t_end.record(main)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_begin.elapsed_time(t_end)
     pack_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
-    unpack_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    table_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    unpack_ms = sum(e[2].elapsed_time(e[3]) for e in evs) / args.steps
+    pack_launches, unpack_launches = launches['pack'] // args.steps, launches['unpack'] // args.steps
 
-    # correctness of what was just timed: the last two tensors unpacked, and the status word
-    for i in (len(slots) - 2, len(slots) - 1):
-        assert torch.equal(out[i & 1].view(torch.int16), slots[i].x.view(torch.int16)), 'round trip not bit-exact'
-    codec.check_device_status(dev)
+    # ---- parity of what was just timed: every tensor, full size, bit for bit -------------
+    mismatches = []
 
-    # ---- end to end through the public API, K/V in pinned host memory -------------------
-    cfg = StubConfig(LAYERS)
-    host_in = [s.x.to('cpu').pin_memory() for s in slots]
-    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(2)]
-    e2e_steps = max(1, min(args.steps, 3))
+    def check_layer(li):
+        for wi in range(2):
+            if not torch.equal(out[wi].view(torch.int16), slots[li]['x'][wi].view(torch.int16)):
+                mismatches.append((li, wi))
 
+    step(check=check_layer)
+    torch.cuda.synchronize(dev)
+    st_word = int(status[0].item())
+    round_trip_ok = not mismatches and st_word == 0
+    n_esc = 0
+    code_bytes = 0
+    nbits_hist = {n: 0 for n in (1, 2, 3, 4)}
+    comp_bytes = 0
+    for ent in slots:
+        for span in ('a', 'b'):
+            for s in ent[span]:
+                e = int(s.offsets[-1].item())
+                n_esc += e
+                code_bytes += s.x.numel() * s.nbits // 8
+                nbits_hist[s.nbits] += 1
+                comp_bytes += s.x.numel() + s.x.numel() * s.nbits // 8 + e + 4 * per * S4_HEADS * s.n_blocks
+    windows_a = [[(s.right, s.nbits) for s in ent['a']] for ent in slots]
+    windows_b = [[(s.right, s.nbits) for s in ent['b']] for ent in slots]
+    changed = sum(1 for a, b in zip(windows_a, windows_b) for x, y in zip(a, b) if x != y)
+    # every rank must have adopted the same windows (they all saw the all-reduced histogram)
+    wb = torch.tensor(windows_b, dtype=torch.int32, device=dev).flatten()
+    windows_agree = True
+    if world > 1:
+        lo, hi = wb.clone(), wb.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        windows_agree = bool(torch.equal(lo, hi))
+
+    # ---- reduced replica through the cache API, sharded over the NCCL ranks, against the oracle ----
+    replica = replica_parity(dev, world, rank)
+
+    # ---- end to end through the public API with host buffers ----------------------------
+    e2e = e2e_leg(args, dev, world, rank, slots, calib, per, b0)
+
+    stats = torch.tensor([total_ms, pack_ms, unpack_ms, table_ms, e2e['ms'], e2e['copy_ms'],
+                          0.0 if round_trip_ok else 1.0, 0.0 if replica['ok'] else 1.0], dtype=torch.float64, device=dev)
+    sums = torch.tensor([float(n_esc), float(comp_bytes), float(code_bytes)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    total_ms, pack_ms, unpack_ms, table_ms, e2e_ms, copy_ms, rt_bad, rep_bad = stats.tolist()
+    n_esc_all, comp_all, code_all = sums.tolist()
+    per_shard = None
+    if world > 1:
+        mine = torch.tensor([pack_ms, unpack_ms], dtype=torch.float64, device=dev)
+        mine[0] = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+        mine[1] = sum(e[2].elapsed_time(e[3]) for e in evs) / args.steps
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        per_shard = [[round(2.0 * n_elems / (g[0].item() * 1e-3) / 1e9, 1),
+                      round(2.0 * n_elems / (g[1].item() * 1e-3) / 1e9, 1)] for g in gathered]
+    if rank != 0:
+        return {}
+
+    bf16_bytes = 2.0 * n_elems                                   # per rank
+    ms_per_step = total_ms / args.steps
+    value = world * 2 * bf16_bytes / (ms_per_step * 1e-3) / 1e9
+    alg = 2.0 * n_elems + n_elems + code_bytes + n_esc           # per rank: read bf16, write planes + escapes
+    peak, peak_kind = measured_hbm_peak()
+    ach_pack = alg / (pack_ms * 1e-3) / 1e9
+    ach_unpack = alg / (unpack_ms * 1e-3) / 1e9
+    pack_calls = pack_launches // 2
+    line = {
+        'metric': METRIC, 'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+        'warmup': warm, 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
+        'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
+        'config': workload_config(world),
+        'workload_stats': {'layers': n_layers, 'nbits_histogram': {str(k): v for k, v in nbits_hist.items()},
+                           'escape_fraction': round(n_esc_all / (world * n_elems), 5),
+                           'adjuster': {'spans_whose_window_changed': changed,
+                                        'adoptions_during_run': adopted['changes'],
+                                        'windows_agree_across_ranks': windows_agree,
+                                        'example_layer0': {'tokens_0_4095': windows_a[0],
+                                                           'tokens_4096_8191': windows_b[0]}}},
+        'pack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (pack_ms * 1e-3) / 1e9, 1),
+        'unpack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (unpack_ms * 1e-3) / 1e9, 1),
+        'pack_bf16_equiv_GBps_whole_box': round(world * bf16_bytes / (pack_ms * 1e-3) / 1e9, 1),
+        'unpack_bf16_equiv_GBps_whole_box': round(world * bf16_bytes / (unpack_ms * 1e-3) / 1e9, 1),
+        'per_shard_pack_unpack_GBps': per_shard,
+        'compression_ratio': round(comp_all / (2.0 * world * n_elems), 5),
+        'roofline': {'bound': 'hbm', 'kernel': 'k_pack_pipe (+ k_compact_units)', 'achieved': round(ach_pack, 1),
+                     'peak': peak, 'unit': 'GB/s', 'frac': round(ach_pack / peak, 4), 'peak_source': peak_kind,
+                     'traffic': round(PACK_DRAM_BYTES_PER_ELEM * n_elems / pack_calls),
+                     'algorithmic_bytes_per_launch': round(alg / pack_calls),
+                     'avg_launch_us': round(pack_ms * 1e3 / pack_calls, 2),
+                     'launch': 'one adacode_pack_jobs call: K and V of one 4096-token span'},
+        'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_pipe', 'achieved': round(ach_unpack, 1),
+                            'peak': peak, 'unit': 'GB/s', 'frac': round(ach_unpack / peak, 4),
+                            'avg_launch_us': round(unpack_ms * 1e3 / unpack_launches, 2),
+                            'launch': 'one adacode_unpack_jobs call: K and V of a layer, 64 segments each'},
+        'table_refresh_ms_per_step': round(table_ms, 3),
+        'parity': {'full_size_round_trip': 'ok' if rt_bad == 0 else f'MISMATCH {mismatches[:4]} status {st_word}',
+                   'replica_vs_oracle': 'ok' if rep_bad == 0 else 'MISMATCH', 'replica': replica['detail']},
+        'e2e': {'value': round(world * e2e['bytes'] * 2 / (e2e_ms * 1e-3) / 1e9, 2), 'unit': 'GB/s',
+                'h2d_bytes_per_step': int(e2e['bytes']), 'd2h_bytes_per_step': int(e2e['bytes']),
+                'ms_per_step': round(e2e_ms, 2), 'layers': e2e['layers'],
+                'api': 'Float11Cache.update (8192-token prefill per layer) + materialize_layer',
+                'copy_only_GBps': round(world * e2e['bytes'] * 2 / (copy_ms * 1e-3) / 1e9, 2)},
+        'gpu_launches': args.steps * (pack_launches + unpack_launches + 1),
+        'clocks': clocks,
+    }
+    if world == 1:
+        spans = cpu_sample()
+        cpu_dt, cpu_n, cpu_threads = cpu_round_trip(spans, repeats=2)
+        line['cpu_baseline'] = {'value': round(2 * 2 * cpu_n / cpu_dt / 1e9, 3), 'unit': 'GB/s', 'cores': cpu_threads,
+                                'kind': 'port', 'sample': CPU_SAMPLE_TEXT}
+    return line
+
+
+def replica_parity(dev, world: int, rank: int) -> dict:
+    """A reduced replica of the stress schedule through the product's sharded path: every rank runs
+    Float11Cache(hist_reduce=all-reduce over the ranks) on its sequences -- a 512-token prefill, then
+    single-token appends with sigma doubled for heads 4-7, so that blocks are staged exactly on adjust
+    steps and the adjuster (fed the histogram of ALL ranks) changes the window.  Rank 0 then gathers
+    every shard's segments, merges them (merge_shard_segments) and compares every byte stream with
+    the CPU oracle's pack of the UNSHARDED block, and the adopted windows with the oracle's choice from
+    the unsharded histogram."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from adacode_b200 import Float11Cache
+    from adacode_b200.sharding import HistogramAllReduce, merge_shard_segments
+    from oracle import float11_oracle as O
+    import kv_synth
+
+    n_layers, per, H, D, prefill, appends, shift = 2, 2, S4_HEADS, S4_DIM, 512, 300, 512
+    total = prefill + appends
+    b0 = rank * per
+    tabs, xs = {}, {}
+    calib = {}
+    for l in range(n_layers):
+        for wi, which in enumerate(('k', 'v')):
+            sigma, offset = kv_synth.channel_tables(H, D, seed=7000 + 2 * l + wi, key_offset=(which == 'k'))
+            tabs[(l, wi)] = (sigma, offset)
+            cal = kv_synth.kv_tensor(900 + 2 * l + wi, (1, H, 1024, D), sigma, offset, 'cpu')
+            calib[(l, wi)] = calibrate_from(O.exponent_hist(cal))
+
+    def gen(l, wi, b_start, nb, device):
+        sigma, offset = tabs[(l, wi)]
+        right, nbits = calib[(l, wi)]
+        return kv_synth.kv_tensor(800 + 2 * l + wi, (nb, H, total, D), sigma, offset, device, b0=b_start,
+                                  shift_from=shift, shift_heads=S4_SHIFT_HEADS, shift_scale=16.0,
+                                  escapes=(right - 2 ** nbits + 1, right, S4_P_WINDOW, S4_P_ZERO))
+
+    for l in range(n_layers):
+        for wi in range(2):
+            xs[(l, wi)] = gen(l, wi, b0, per, dev)
+    cache = Float11Cache(StubConfig(n_layers), right=[(calib[(l, 0)][0], calib[(l, 1)][0]) for l in range(n_layers)],
+                         exp_bits=[(calib[(l, 0)][1], calib[(l, 1)][1]) for l in range(n_layers)], need_adjust=True,
+                         update_steps=128, residual_length=0, block_size=BLOCK, layout='segmented_tiled',
+                         hist_reduce=HistogramAllReduce() if world > 1 else None)
+    for l in range(n_layers):
+        cache.update(xs[(l, 0)][:, :, :prefill], xs[(l, 1)][:, :, :prefill], l)
+    dk = dv = None
+    for t in range(prefill, total):
+        for l in range(n_layers):
+            dk, dv = cache.update(xs[(l, 0)][:, :, t:t + 1], xs[(l, 1)][:, :, t:t + 1], l)
+    ok = torch.equal(dk.view(torch.int16), xs[(n_layers - 1, 0)].view(torch.int16)) and \
+        torch.equal(dv.view(torch.int16), xs[(n_layers - 1, 1)].view(torch.int16))
+    # export this shard's segments as CPU tensors
+    mine = []
+    for l in range(n_layers):
+        layer = cache.layers[l]
+        for segs in (layer._key_segments, layer._value_segments):
+            states = []
+            for seg in segs:
+                st = seg.export_state()
+                states.append({k: (v.cpu() if torch.is_tensor(v) else (str(v) if k == 'device' else v))
+                               for k, v in st.items()})
+            mine.append(states)
+    gathered = [mine]
+    if world > 1:
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object(mine, gathered, dst=0)
+    detail = {'schedule': f'{n_layers} layers, {per} sequences per rank, {prefill}-token prefill + {appends} single-token '
+                          'appends, sigma x16 for heads 4-7 from the first appended token',
+              'ranks': world}
+    if rank != 0:
+        return {'ok': ok, 'detail': detail}
+    seg_count, window_changes, bad = 0, 0, []
+    for ti in range(len(mine)):
+        l, wi = divmod(ti, 2)
+        full = O.as_u16(gen(l, wi, 0, per * world, 'cpu'))
+        n_seg = len(gathered[0][ti])
+        prev = None
+        for j in range(n_seg):
+            shards = [gathered[r][ti][j] for r in range(world)]
+            merged = merge_shard_segments(shards) if world > 1 else shards[0]
+            right, nbits = int(merged['right']), int(merged['nbits'])
+            blk = np.ascontiguousarray(full[:, :, j * BLOCK:(j + 1) * BLOCK])
+            ref = O.pack_block(blk, right, nbits, need_hist=True)
+            same = (np.array_equal(merged['sign_mass_data'].numpy(), ref.sign_mass_data)
+                    and np.array_equal(merged['exp_data'].numpy(), ref.exp_data)
+                    and np.array_equal(merged['invalid_exp'].numpy(), ref.invalid_exp)
+                    and np.array_equal(merged['tile_invalid_base'].numpy(), ref.tile_invalid_base))
+            if not same:
+                bad.append((l, wi, j, 'bytes'))
+            # blocks staged in decode are packed with the window chosen from their own whole-batch histogram
+            if j >= prefill // BLOCK and (right, nbits) != O.choose_params(ref.hist):
+                bad.append((l, wi, j, 'window'))
+            if prev is not None and prev != (right, nbits):
+                window_changes += 1
+            prev = (right, nbits)
+            seg_count += 1
+    detail.update(segments_checked=seg_count, window_changes=window_changes,
+                  adjuster_collectives=getattr(cache.layers[0].hist_reduce, 'calls', 0) if world > 1 else 0,
+                  mismatches=bad[:4])
+    return {'ok': ok and not bad, 'detail': detail}
+
+
+def e2e_leg(args, dev, world: int, rank: int, slots, calib, per: int, b0: int) -> dict:
+    """Host K/V -> device -> Float11Cache.update (pack) -> materialize_layer (unpack) -> host, on the
+    first few layers of the workload (as many as give about 4 GB of K+V per rank); the copies of
+    neighbouring layers run on their own streams.  Also a copy-only pass over the same buffers: the
+    host<->device ceiling at this N."""
+    import torch
+    from adacode_b200 import Float11Cache
+    main = torch.cuda.current_stream(dev)
+    layer_bytes = 2 * slots[0]['x'][0].numel() * 2
+    n_l = max(2, min(len(slots), int(4.3e9 // layer_bytes)))
+    n_l = min(n_l, len(slots))
+    cfg = StubConfig(n_l)
+    rights = [(calib[(l, 'k')][0], calib[(l, 'v')][0]) for l in range(n_l)]
+    nbits = [(calib[(l, 'k')][1], calib[(l, 'v')][1]) for l in range(n_l)]
+    host_in = [[x.to('cpu').pin_memory() for x in slots[l]['x']] for l in range(n_l)]
+    host_out = [torch.empty_like(host_in[0][0]).pin_memory() for _ in range(2)]
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    stage = [[torch.empty_like(slots[0].x) for _ in range(2)] for _ in range(2)]      # double-buffered K, V
+    stage = [[torch.empty_like(slots[0]['x'][0]) for _ in range(2)] for _ in range(2)]      # double-buffered K, V
+    steps = max(1, min(args.steps, 3))
 
-    def e2e_step():
-        """Host K/V -> device -> Float11Cache.update (pack) -> materialize_layer (unpack) -> host.
-        The copies of neighbouring layers run on their own streams so that PCIe traffic in both
-        directions overlaps the kernels; per-layer dense mirrors keep a layer's unpacked K/V alive
-        while it is copied out."""
-        main = torch.cuda.current_stream(dev)
-        cache = Float11Cache(cfg, right=rights, exp_bits=nbits, need_adjust=True, update_steps=128,
-                             residual_length=0, block_size=BLOCK, layout='segmented_tiled', dense_workspace='layer')
+    def run(with_codec: bool):
+        cache = None
+        if with_codec:
+            cache = Float11Cache(cfg, right=rights, exp_bits=nbits, need_adjust=True, update_steps=128,
+                                 residual_length=0, block_size=BLOCK, layout='segmented_tiled', dense_workspace='layer')
         ready = [torch.cuda.Event() for _ in range(2)]
         free = [torch.cuda.Event() for _ in range(2)]
 
@@ -359,130 +794,455 @@ def run_gpu_arm(args) -> None:
             with torch.cuda.stream(copy_in):
                 if l >= 2:
                     copy_in.wait_event(free[buf])
-                stage[buf][0].copy_(host_in[2 * l], non_blocking=True)
-                stage[buf][1].copy_(host_in[2 * l + 1], non_blocking=True)
+                stage[buf][0].copy_(host_in[l][0], non_blocking=True)
+                stage[buf][1].copy_(host_in[l][1], non_blocking=True)
                 ready[buf].record(copy_in)
 
         upload(0)
-        for l in range(LAYERS):
+        for l in range(n_l):
             buf = l & 1
-            if l + 1 < LAYERS:
+            if l + 1 < n_l:
                 upload(l + 1)
             main.wait_event(ready[buf])
-            cache.update(stage[buf][0], stage[buf][1], l)
-            free[buf].record(main)
-            dk, dv = cache.materialize_layer(l)
+            if with_codec:
+                cache.update(stage[buf][0], stage[buf][1], l)
+                free[buf].record(main)
+                dk, dv = cache.materialize_layer(l)
+            else:
+                dk, dv = stage[buf]
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(done)
                 host_out[0].copy_(dk, non_blocking=True)
                 host_out[1].copy_(dv, non_blocking=True)
+                if not with_codec:
+                    free[buf].record(copy_out)
         torch.cuda.synchronize(dev)
         return cache
 
-    # a step hands its cache back before the next one starts (a server recycles its cache pool):
-    # otherwise two 36-layer caches are alive at once and every step pays fresh cudaMalloc calls
-    cache = e2e_step()
-    cache.synchronize_and_release()
-    cache = e2e_step()
-    barrier()
-    w0 = torch.cuda.Event(enable_timing=True)
-    w1 = torch.cuda.Event(enable_timing=True)
-    w0.record()
-    for _ in range(e2e_steps):
-        cache.synchronize_and_release()
-        cache = e2e_step()
-    w1.record()
-    barrier()
-    e2e_ms = w0.elapsed_time(w1) / e2e_steps
-    assert torch.equal(host_out[1].view(torch.int16), host_in[-1].view(torch.int16)), 'e2e round trip not bit-exact'
-    mem = cache.get_memory()
-    ratio = mem['kv_compressed_memory'] / mem['kv_original_memory']
-
-    # ---- optional fused path: one decode step of attention over layer 0 of that cache --------------
-    # (32 query heads on 8 KV heads, every cached token attended to), against unpacking K and V and
-    # running torch SDPA on the dense tensors; several launches back to back per sample
-    import torch.nn.functional as F
-    layer0 = cache.layers[0]
-    q = (torch.randn(1, 32, 1, HEAD_DIM, device=dev) * 0.3).to(torch.bfloat16)
-    dk = torch.empty((1, KV_HEADS, PROMPT, HEAD_DIM), dtype=torch.bfloat16, device=dev)
-    dv = torch.empty_like(dk)
-
-    def attn_fused():
-        return layer0.decode_attention(q)
-
-    def attn_materialised():
-        codec.unpack_segments(layer0._key_segments, dk, table=layer0._segment_table('k', layer0._key_segments))
-        codec.unpack_segments(layer0._value_segments, dv, table=layer0._segment_table('v', layer0._value_segments))
-        return F.scaled_dot_product_attention(q, dk, dv, enable_gqa=True)
-
-    def time_us(fn, inner=16):
-        for _ in range(3):
-            fn()
+    def timed(with_codec: bool) -> float:
+        cache = run(with_codec)
+        if cache is not None:
+            cache.synchronize_and_release()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+        a.record(main)
+        for _ in range(steps):
+            cache = run(with_codec)
+            if cache is not None and _ < steps - 1:
+                cache.synchronize_and_release()
+        b.record(main)
+        torch.cuda.synchronize(dev)
+        if with_codec:
+            assert torch.equal(host_out[1].view(torch.int16), host_in[n_l - 1][1].view(torch.int16)), \
+                'e2e round trip not bit-exact'
+            cache.synchronize_and_release()
+        return a.elapsed_time(b) / steps
+
+    ms = timed(True)
+    copy_ms = timed(False)
+    return {'ms': ms, 'copy_ms': copy_ms, 'bytes': float(n_l * layer_bytes), 'layers': n_l}
+
+
+# --------------------------------------------------------------------------------------
+# further configurations (N = 1)
+# --------------------------------------------------------------------------------------
+
+def _time_us(fn, dev, inner: int = 8, warm: int = 2) -> float:
+    import torch
+    for _ in range(warm):
         fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fn()
+    a.record()
+    for _ in range(inner):
+        fn()
+    b.record()
+    torch.cuda.synchronize(dev)
+    return a.elapsed_time(b) * 1e3 / inner
+
+
+def config1_block(args, dev) -> dict:
+    """Qwen3-4B-shaped cache: 36 layers x K,V [1, 8, 20480, 128] packed once (one launch per layer),
+    unpacked again; every packed byte stream compared with the CPU oracle's; then 128 single-token
+    appends per layer through the cache API."""
+    import kv_synth
+    import numpy as np
+    import torch
+    from adacode_b200 import Float11Cache, _lib, codec
+    from oracle import float11_oracle as O
+    L = _lib.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    total = C1_PROMPT + C1_DECODE
+    data, wins = [], []
+    for l in range(C1_LAYERS):
+        mu = -1.0 + 2.0 * l / (C1_LAYERS - 1)
+        pair, win = [], []
+        for wi, which in enumerate(('k', 'v')):
+            sigma, offset = kv_synth.channel_tables(C1_HEADS, C1_DIM, seed=1000 + 2 * l + wi, mu=mu,
+                                                    key_offset=(which == 'k'))
+            cal = kv_synth.kv_tensor(50000 + 2 * l + wi, (1, C1_HEADS, 1024, C1_DIM), sigma, offset, 'cpu')
+            win.append(calibrate_from(O.exponent_hist(cal)))
+            pair.append(kv_synth.kv_tensor(2 * l + wi, (1, C1_HEADS, total, C1_DIM), sigma, offset, dev))
+        data.append(pair)
+        wins.append(win)
+    slots = [[SpanSlots(data[l][wi][:, :, :C1_PROMPT], wins[l][wi][0], wins[l][wi][1], dev) for wi in range(2)]
+             for l in range(C1_LAYERS)]
+    n_elems = sum(s.x.numel() for pair in slots for s in pair)
+    tiles = 2 * C1_HEADS * (C1_PROMPT // BLOCK)
+    ws = torch.zeros(L.adacode_pack_workspace_bytes(tiles, BLOCK * C1_DIM), dtype=torch.uint8, device=dev)
+    hists = torch.zeros((C1_LAYERS, 2, 256), dtype=torch.int32, device=dev)
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    out = [torch.empty((1, C1_HEADS, C1_PROMPT, C1_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    calls = {'pack': 0}
+
+    def pack_all():
+        for l, pair in enumerate(slots):
+            groups = [pair] if pair[0].nbits == pair[1].nbits else [[pair[0]], [pair[1]]]
+            for grp in groups:
+                jobs = (_lib.PackJob * len(grp))()
+                for jb, s in zip(jobs, grp):
+                    fill_pack_job(jb, s, hists[l, pair.index(s)].data_ptr())
+                _lib.check(L.adacode_pack_jobs(ctypes.addressof(jobs), len(grp), 1, C1_HEADS, BLOCK, C1_DIM,
+                                               grp[0].nbits, ws.data_ptr(), ws.numel(), status.data_ptr(), stream),
+                           'adacode_pack_jobs')
+                calls['pack'] += 1
+
+    def unpack_pair(pair):
+        for wi, s in enumerate(pair):
+            db, dh, ds, _ = out[wi].stride()
+            _lib.check(L.adacode_unpack_tiles(s.sign_mant.data_ptr(), s.codes.data_ptr(), s.escapes.data_ptr(), s.cap,
+                                              s.tile_base.data_ptr(), s.offsets.data_ptr(), 1, C1_HEADS, s.n_blocks,
+                                              BLOCK, C1_DIM, s.left, s.nbits, out[wi].data_ptr(), db, dh, ds,
+                                              status.data_ptr(), stream), 'adacode_unpack_tiles')
+
+    def unpack_all():
+        for pair in slots:
+            unpack_pair(pair)
+
+    steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        hists.zero_()
+        pack_all()
+        unpack_all()
+    torch.cuda.synchronize(dev)
+    calls['pack'] = 0
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ev[0].record()
+    for _ in range(steps):
+        pack_all()
+    ev[1].record()
+    for _ in range(steps):
+        unpack_all()
+    ev[2].record()
+    torch.cuda.synchronize(dev)
+    pack_ms, unpack_ms = ev[0].elapsed_time(ev[1]) / steps, ev[1].elapsed_time(ev[2]) / steps
+    pack_calls = calls['pack'] // steps
+
+    # byte parity of all 72 tensors against the oracle, and the round trip, outside the timed region
+    bad = []
+    n_esc = code_bytes = 0
+    for l, pair in enumerate(slots):
+        unpack_pair(pair)
+        for wi, s in enumerate(pair):
+            if not torch.equal(out[wi].view(torch.int16), s.x.view(torch.int16)):
+                bad.append((l, wi, 'round trip'))
+            x_cpu = O.as_u16(s.x)
+            nb = s.n_blocks
+            blocks = np.ascontiguousarray(x_cpu.reshape(1, C1_HEADS, nb, BLOCK, C1_DIM).transpose(2, 0, 1, 3, 4)
+                                          .reshape(nb, C1_HEADS, BLOCK, C1_DIM))
+            # the oracle packs block j as a batch entry: planes come out block-major like the kernel's
+            ref = O.pack_block(blocks, s.right, s.nbits)
+            total_esc = int(s.offsets[-1].item())
+            n_esc += total_esc
+            code_bytes += s.x.numel() * s.nbits // 8
+            # the oracle counted the escapes of all blocks as one segment: rebase per block
+            ref_base = ref.tile_invalid_base.reshape(nb, C1_HEADS).astype(np.int64)
+            cum_end = ref_base[:, -1].copy()
+            run = np.concatenate(([0], cum_end[:-1]))
+            ref_base = (ref_base - run[:, None]).astype(np.int32)
+            same = (np.array_equal(s.sign_mant.cpu().numpy(), ref.sign_mass_data)
+                    and np.array_equal(s.codes[: s.x.numel() * s.nbits // 8].cpu().numpy(), ref.exp_data)
+                    and np.array_equal(s.escapes[:total_esc].cpu().numpy(), ref.invalid_exp)
+                    and np.array_equal(s.tile_base.cpu().numpy().reshape(nb, C1_HEADS), ref_base)
+                    and np.array_equal(s.offsets.cpu().numpy(), np.concatenate(([0], cum_end))))
+            if not same:
+                bad.append((l, wi, 'bytes'))
+    st_word = int(status[0].item())
+    alg = 3.0 * n_elems + code_bytes + n_esc
+    peak, _ = measured_hbm_peak()
+    res = {
+        'workload': 'config1: Qwen3-4B-shaped cache, 36 layers x K,V [1,8,20480,128]; prefill packed by one launch per layer '
+                    '(K and V together), unpacked by one launch per tensor',
+        'pack_bf16_equiv_GBps': round(2.0 * n_elems / (pack_ms * 1e-3) / 1e9, 1),
+        'unpack_bf16_equiv_GBps': round(2.0 * n_elems / (unpack_ms * 1e-3) / 1e9, 1),
+        'roofline_pack_frac': round(alg / (pack_ms * 1e-3) / 1e9 / peak, 4),
+        'roofline_unpack_frac': round(alg / (unpack_ms * 1e-3) / 1e9 / peak, 4),
+        'pack_call_us': round(pack_ms * 1e3 / pack_calls, 2), 'unpack_launch_us': round(unpack_ms * 1e3 / 72, 2),
+        'escape_fraction': round(n_esc / n_elems, 5),
+        'compression_ratio': round((n_elems + code_bytes + n_esc + 4 * C1_HEADS * (C1_PROMPT // BLOCK) * 72)
+                                   / (2.0 * n_elems), 5),
+        'byte_parity_72_tensors_vs_oracle': 'ok' if not bad and st_word == 0 else f'MISMATCH {bad[:4]} status {st_word}',
+    }
+    del slots, out, ws
+    torch.cuda.empty_cache()
+
+    # ---- decode half: 128 single-token appends per layer through the cache API ----------
+    cfg = StubConfig(C1_LAYERS)
+    rights = [(w[0][0], w[1][0]) for w in wins]
+    nb = [(w[0][1], w[1][1]) for w in wins]
+    q = (torch.randn(1, 32, 1, C1_DIM, device=dev) * 0.3).to(torch.bfloat16)
+    decode = {}
+    for mode in ('layer', 'shared', 'fused'):
+        cache = Float11Cache(cfg, right=rights, exp_bits=nb, need_adjust=True, update_steps=128, residual_length=0,
+                             block_size=BLOCK, layout='segmented_tiled',
+                             dense_workspace='layer' if mode == 'layer' else 'shared')
+        for l in range(C1_LAYERS):
+            cache.update(data[l][0][:, :, :C1_PROMPT], data[l][1][:, :, :C1_PROMPT], l)
+        torch.cuda.synchronize(dev)
+        cache._fused_decode = (mode == 'fused')
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dk = dv = None
         a.record()
-        for _ in range(inner):
-            fn()
+        for t in range(C1_PROMPT, total):
+            for l in range(C1_LAYERS):
+                dk, dv = cache.update(data[l][0][:, :, t:t + 1], data[l][1][:, :, t:t + 1], l)
+                if mode == 'fused':
+                    cache.layers[l].decode_attention(q)
         b.record()
         torch.cuda.synchronize(dev)
-        return a.elapsed_time(b) * 1e3 / inner
+        cache._fused_decode = False
+        ms = a.elapsed_time(b) / C1_DECODE
+        if mode != 'fused':
+            ok = torch.equal(dk.view(torch.int16), data[-1][0].view(torch.int16)) and \
+                torch.equal(dv.view(torch.int16), data[-1][1].view(torch.int16))
+        else:
+            fk, fv = cache.materialize_layer(C1_LAYERS - 1)
+            ok = torch.equal(fk.view(torch.int16), data[-1][0].view(torch.int16)) and \
+                torch.equal(fv.view(torch.int16), data[-1][1].view(torch.int16))
+        mem = cache.get_memory()
+        lay = cache.layers[0]
+        decode[mode] = {'ms_per_decode_step': round(ms, 3), 'dense_equals_input': bool(ok),
+                        'segments_per_layer': len(lay._key_segments), 'adjust_recompresses': int(lay._adjust_recompresses),
+                        'staged_dense_residual_tokens': int(lay._res_k.length)}
+        if mode == 'shared':
+            decode['compression_ratio_after_decode'] = round(mem['kv_compressed_memory'] / mem['kv_original_memory'], 5)
+        cache.synchronize_and_release()
+        del cache
+        torch.cuda.empty_cache()
+    decode['note'] = ("'layer': update with a per-layer dense mirror; 'shared': update with one shared dense workspace "
+                      "(every layer unpacked again each step); 'fused': update only appends and decode_attention reads "
+                      'the packed planes (attention of 32 query heads included)')
+    res['decode_128_appends'] = decode
+    return res
 
-    attn_diff = (attn_fused().float() - attn_materialised().float()).abs().max().item()
-    attn_us = (time_us(attn_fused), time_us(attn_materialised))
 
-    times = torch.tensor([total_ms, pack_ms, unpack_ms, e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, pack_ms, unpack_ms, e2e_ms = times.tolist()
+def config3_block(args, dev) -> dict:
+    """DeepSeek-V2-Lite-shaped MLA cache: 27 layers, latent [8, 1, 16384, 512] + rope key [8, 1, 16384, 64]
+    (magnitudes modulated sinusoidally along the sequence); pack, unpack through MLAFloat11Cache with
+    the rope key compressed (primary) and kept dense (secondary); kernel throughput per tile shape."""
+    import kv_synth
+    import numpy as np
+    import torch
+    from adacode_b200 import MLAFloat11Cache, codec
+    from oracle import float11_oracle as O
+    LAYERS3, B, S, DL, DR = 27, 8, 16384, 512, 64
+    pos = torch.arange(S, dtype=torch.float32).view(S, 1)
+    freq = torch.exp(-torch.arange(DR, dtype=torch.float32) / DR * 6.0).view(1, DR)
+    modulation = 1.0 + torch.sin(pos * freq)
+    lat, rope, wins = [], [], []
+    for l in range(LAYERS3):
+        sl, ol = kv_synth.channel_tables(1, DL, seed=3000 + 2 * l, mu=-0.5, s=0.8)
+        sr, orr = kv_synth.channel_tables(1, DR, seed=3001 + 2 * l, mu=-0.5, s=0.8)
+        lat.append(kv_synth.kv_tensor(30000 + 2 * l, (B, 1, S, DL), sl, ol, dev))
+        rope.append(kv_synth.kv_tensor(30001 + 2 * l, (B, 1, S, DR), sr, orr, dev, modulation=modulation))
+        cl = kv_synth.kv_tensor(39000 + 2 * l, (1, 1, 1024, DL), sl, ol, 'cpu')
+        cr = kv_synth.kv_tensor(39001 + 2 * l, (1, 1, 1024, DR), sr, orr, 'cpu', modulation=modulation)
+        wins.append((calibrate_from(O.exponent_hist(cl)), calibrate_from(O.exponent_hist(cr))))
+    peak, _ = measured_hbm_peak()
+    res = {'workload': 'config3: MLA latent cache, 27 layers, latent [8,1,16384,512] + rope key [8,1,16384,64]'}
 
-    if rank == 0:
-        bf16_bytes = 2.0 * n_elems
-        ms_per_step = total_ms / args.steps
-        value = world * 2 * bf16_bytes / (ms_per_step * 1e-3) / 1e9
-        alg_pack = 2.0 * n_elems + n_elems + code_bytes + n_esc          # read bf16, write planes + escapes
-        peak, peak_kind = measured_hbm_peak()
-        launches = len(slots)
-        ach_pack = alg_pack / (pack_ms * 1e-3) / 1e9
-        ach_unpack = alg_pack / (unpack_ms * 1e-3) / 1e9
-        cpu_dt, cpu_n, cpu_threads = cpu_round_trip(PROMPT // BLOCK, 2, repeats=max(1, LAYERS // 6))
-        line = {
-            'metric': METRIC, 'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
-            'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'u16', 'data': 'synthetic',
-            'config': {'workload': WORKLOAD, 'per_gpu': 'one 20480-token sequence per GPU', 'block_size': BLOCK,
-                       'l2': 'inputs (3.0 GB per GPU) exceed L2, no flush needed',
-                       'streams': 'K and V of a layer run on two streams',
-                       'nbits_histogram': {str(n): sum(1 for s in slots if s.nbits == n) for n in (1, 2, 3, 4)},
-                       'escape_fraction': round(n_esc / n_elems, 5)},
-            'pack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (pack_ms * 1e-3) / 1e9, 1),
-            'unpack_bf16_equiv_GBps_per_gpu': round(bf16_bytes / (unpack_ms * 1e-3) / 1e9, 1),
-            'compression_ratio': round(ratio, 5),
-            'roofline': {'bound': 'hbm', 'kernel': 'k_pack_pipe (+ k_compact_units)', 'achieved': round(ach_pack, 1),
-                         'peak': peak, 'unit': 'GB/s', 'frac': round(ach_pack / peak, 4), 'peak_source': peak_kind,
-                         'traffic': None if PACK_DRAM_BYTES_PER_ELEM is None else
-                         round(PACK_DRAM_BYTES_PER_ELEM * n_elems / launches),
-                         'algorithmic_bytes_per_launch': round(alg_pack / launches),
-                         'avg_launch_us': round(pack_ms * 1e3 / launches, 2)},
-            'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_pipe', 'achieved': round(ach_unpack, 1),
-                                'peak': peak, 'unit': 'GB/s', 'frac': round(ach_unpack / peak, 4),
-                                'avg_launch_us': round(unpack_ms * 1e3 / launches, 2)},
-            'cpu_baseline': {'value': round(2 * 2 * cpu_n / cpu_dt / 1e9, 3), 'unit': 'GB/s', 'cores': cpu_threads,
-                             'kind': 'port', 'sample': f'{max(1, LAYERS // 6)} of {LAYERS} layers, K and V '
-                             '[1,8,20480,128], packed and unpacked by the OpenMP oracle'},
-            'e2e': {'value': round(world * 2 * bf16_bytes / (e2e_ms * 1e-3) / 1e9, 2), 'unit': 'GB/s',
-                    'h2d_bytes_per_step': int(bf16_bytes), 'd2h_bytes_per_step': int(bf16_bytes),
-                    'ms_per_step': round(e2e_ms, 2), 'api': 'Float11Cache.update + materialize_layer'},
-            'decode_attention': {'shape': f'q [1,32,1,{HEAD_DIM}] over one layer of the cache ({PROMPT} tokens)',
-                                 'fused_us': round(attn_us[0], 1), 'unpack_then_sdpa_us': round(attn_us[1], 1),
-                                 'max_abs_diff': round(attn_diff, 5)},
-            'gpu_launches': args.steps * len(slots) * 3,
-            'clocks': clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    # kernel throughput per tile shape (one launch per tensor, all 128 blocks)
+    for name, tensors, widx in (('latent_D512', lat, 0), ('rope_D64', rope, 1)):
+        chunks = [codec.pack_blocks(x, wins[l][widx][0], wins[l][widx][1], BLOCK)[0] for l, x in enumerate(tensors)]
+        n = sum(x.numel() for x in tensors)
+        esc = sum(c.n_escapes for c in chunks)
+        codes = sum(x.numel() * c.nbits // 8 for x, c in zip(tensors, chunks))
+        outb = torch.empty_like(tensors[0])
+
+        def pack_all():
+            for l, x in enumerate(tensors):
+                codec.pack_blocks_launch(x, wins[l][widx][0], wins[l][widx][1], BLOCK, need_hist=True,
+                                         escape_capacity=chunks[l].n_escapes + 4096)
+
+        def unpack_all():
+            for c in chunks:
+                codec.unpack_chunk(c, outb)
+
+        t_pack = _time_us(pack_all, dev, inner=3, warm=1)
+        t_unpack = _time_us(unpack_all, dev, inner=3, warm=1)
+        alg = 3.0 * n + codes + esc
+        res[name] = {'pack_bf16_equiv_GBps': round(2.0 * n / (t_pack * 1e-6) / 1e9, 1),
+                     'unpack_bf16_equiv_GBps': round(2.0 * n / (t_unpack * 1e-6) / 1e9, 1),
+                     'roofline_pack_frac': round(alg / (t_pack * 1e-6) / 1e9 / peak, 4),
+                     'roofline_unpack_frac': round(alg / (t_unpack * 1e-6) / 1e9 / peak, 4),
+                     'escape_fraction': round(esc / n, 5),
+                     'nbits_histogram': {str(k): sum(1 for c in chunks if c.nbits == k) for k in (1, 2, 3, 4)}}
+        # byte parity at size against the oracle, three layers
+        bad = []
+        for l in (0, LAYERS3 // 2, LAYERS3 - 1):
+            x_cpu = O.as_u16(tensors[l])
+            D = x_cpu.shape[-1]
+            nbk = S // BLOCK
+            blocks = np.ascontiguousarray(x_cpu.reshape(B, 1, nbk, BLOCK, D).transpose(2, 0, 1, 3, 4).reshape(nbk * B, 1, BLOCK, D))
+            c = chunks[l]
+            ref = O.pack_block(blocks, c.right, c.nbits)
+            if not (np.array_equal(c.sign_mant.reshape(-1).cpu().numpy(), ref.sign_mass_data)
+                    and np.array_equal(c.codes.reshape(-1).cpu().numpy(), ref.exp_data)
+                    and np.array_equal(c.escapes.cpu().numpy(), ref.invalid_exp)):
+                bad.append(l)
+        res[name]['byte_parity_vs_oracle_layers_0_13_26'] = 'ok' if not bad else f'MISMATCH {bad}'
+        del chunks, outb
+        torch.cuda.empty_cache()
+
+    # through the cache API, both modes
+    cfg = StubConfig(LAYERS3, kv_lora_rank=DL, qk_rope_head_dim=DR)
+    for mode, compress_rope in (('compress_rope', True), ('dense_rope', False)):
+        cache = MLAFloat11Cache(cfg, right=[(w[0][0], w[1][0]) for w in wins], exp_bits=[(w[0][1], w[1][1]) for w in wins],
+                                need_adjust=True, update_steps=128, residual_length=0, block_size=BLOCK,
+                                layout='segmented_tiled', compress_rope=compress_rope)
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ok = True
+        a.record()
+        for l in range(LAYERS3):
+            cache.update(lat[l], rope[l], l)
+            dk, dv = cache.materialize_layer(l)
+            if l in (0, LAYERS3 - 1):
+                ok = ok and torch.equal(dk.view(torch.int16), lat[l].view(torch.int16)) and \
+                    torch.equal(dv.view(torch.int16), rope[l].view(torch.int16))
+        b.record()
+        torch.cuda.synchronize(dev)
+        mem = cache.get_memory()
+        n = sum(x.numel() for x in lat) + sum(x.numel() for x in rope)
+        res[mode] = {'update_plus_materialize_ms': round(a.elapsed_time(b), 2),
+                     'bf16_equiv_GBps': round(2 * 2.0 * n / (a.elapsed_time(b) * 1e-3) / 1e9, 1),
+                     'round_trip_bit_exact': bool(ok),
+                     'compression_ratio': round(mem['kv_compressed_memory'] / mem['kv_original_memory'], 5)}
+        cache.synchronize_and_release()
+        del cache
+        torch.cuda.empty_cache()
+    return res
+
+
+def config2_block(args, dev) -> dict:
+    """Llama-3.1-8B-architecture generation: 32 layers, 32 query / 8 KV heads, head_dim 128, hidden 4096,
+    seed-0 random bf16 weights, 32 prompts of 4096 uniform random token ids, 128 greedy tokens, with
+    DynamicCache, with Float11Cache (update returns dense K/V) and with the fused decode attention."""
+    import torch
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+    from adacode_b200 import Float11Cache, hf_attention
+    batch, prompt, new = args.c2_batch, args.c2_prompt, args.c2_new
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.c2_layers,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=128256,
+                      max_position_embeddings=prompt + new + 8, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      tie_word_embeddings=False)
+    name = hf_attention.register()
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = LlamaForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    model.eval()
+    g = torch.Generator('cpu').manual_seed(0)
+    ids = torch.randint(0, 128256, (batch, prompt), generator=g).to(dev)
+
+    def calibrate_cache():
+        """Windows per layer from the K/V of a short calibration prompt (the role the calibration
+        JSON plays for a real checkpoint)."""
+        from adacode_b200 import codec
+        from oracle import float11_oracle as O
+        cal_ids = torch.randint(0, 128256, (2, 512), generator=torch.Generator('cpu').manual_seed(1)).to(dev)
+        dc = DynamicCache()
+        with torch.no_grad():
+            model(cal_ids, past_key_values=dc, use_cache=True, logits_to_keep=1)
+        rights, nbits = [], []
+        for l in range(cfg.num_hidden_layers):
+            k, v = dc.layers[l].keys, dc.layers[l].values
+            wk = calibrate_from(codec.exponent_hist(k.contiguous()).cpu().numpy().astype('int64'))
+            wv = calibrate_from(codec.exponent_hist(v.contiguous()).cpu().numpy().astype('int64'))
+            rights.append((wk[0], wv[0]))
+            nbits.append((wk[1], wv[1]))
+        return rights, nbits
+
+    rights, nbits = calibrate_cache()
+
+    def generate(kind: str):
+        model.config._attn_implementation = name if kind == 'fused' else 'sdpa'
+        if kind == 'dynamic':
+            cache = DynamicCache()
+        else:
+            cache = Float11Cache(cfg, right=rights, exp_bits=nbits, need_adjust=True, update_steps=128,
+                                 residual_length=0, block_size=BLOCK, layout='segmented_tiled', dense_workspace='shared')
+        toks = []
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            out = model(ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+            nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+            toks.append(nxt)
+            torch.cuda.synchronize(dev)
+            t1 = time.perf_counter()
+            ctx = hf_attention.fused_decode(cache) if kind == 'fused' else _null()
+            with ctx:
+                for _ in range(new - 1):
+                    out = model(nxt, past_key_values=cache, use_cache=True)
+                    nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+                    toks.append(nxt)
+            torch.cuda.synchronize(dev)
+            t2 = time.perf_counter()
+        info = {'prefill_s': round(t1 - t0, 3), 'decode_tok_per_s': round(batch * (new - 1) / (t2 - t1), 1),
+                'decode_ms_per_step': round((t2 - t1) * 1e3 / (new - 1), 2)}
+        if kind != 'dynamic':
+            mem = cache.get_memory()
+            info['compression_ratio'] = round(mem['kv_compressed_memory'] / mem['kv_original_memory'], 5)
+            cache.synchronize_and_release()
+        del cache
+        torch.cuda.empty_cache()
+        return torch.cat(toks, dim=1).cpu(), info
+
+    ref, info_ref = generate('dynamic')
+    res = {'workload': f'config2: Llama-3.1-8B architecture ({cfg.num_hidden_layers} layers, 32 q / 8 kv heads, head_dim 128, '
+                       f'hidden 4096, vocab 128256), seed-0 random bf16 weights, {batch} x {prompt}-token prompts, '
+                       f'{new} greedy tokens', 'dynamic_cache': info_ref}
+    for kind in ('update', 'fused'):
+        toks, info = generate(kind)
+        same = (toks == ref)
+        info['token_ids_identical'] = bool(same.all())
+        info['token_agreement'] = round(float(same.float().mean()), 5)
+        if not same.all():
+            first_div = (~same).float().argmax(dim=1)
+            rows = (~same).any(dim=1)
+            info['sequences_that_diverge'] = int(rows.sum())
+            info['first_diverging_position_min'] = int(first_div[rows].min())
+        res['float11_' + kind] = info
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
+class _null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
 
 
 def main() -> None:
@@ -491,6 +1251,13 @@ def main() -> None:
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--blocks', default='', help="comma list of main,config1,config3,config2 (default: all of them "
+                                                 'on one GPU, main on several)')
+    ap.add_argument('--layers', type=int, default=0, help='layers of the primary workload (default: all 36)')
+    ap.add_argument('--c2-batch', type=int, default=32)
+    ap.add_argument('--c2-prompt', type=int, default=4096)
+    ap.add_argument('--c2-new', type=int, default=128)
+    ap.add_argument('--c2-layers', type=int, default=32)
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference_arm(args)

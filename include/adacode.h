@@ -94,6 +94,41 @@ int adacode_pack_tiles(const void *src_bf16, int64_t stride_b, int64_t stride_h,
                        void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
+ * One tensor of a multi-tensor pack launch (adacode_pack_jobs): the arguments of
+ * adacode_pack_tiles that may differ between the tensors of one call.
+ */
+typedef struct adacode_pack_job {
+    const void *src_bf16;        /* [B][H][n_blocks*seq_tile][D], element strides below */
+    int64_t stride_b, stride_h, stride_s;
+    int32_t n_blocks;
+    int32_t right;               /* window (right - 2**nbits + 1, right] */
+    uint8_t *sign_mant;
+    uint8_t *codes;
+    uint8_t *escapes;
+    int64_t escapes_capacity;
+    int32_t *tile_base;
+    int64_t *seg_escape_offsets; /* n_blocks + 1 entries */
+    int32_t *hist256;            /* nullable */
+} adacode_pack_job;
+
+/* Largest n_jobs adacode_pack_jobs / adacode_unpack_jobs accept. */
+int adacode_max_jobs(void);
+
+/*
+ * adacode_pack_tiles for up to adacode_max_jobs() tensors of one shape and code length in ONE
+ * pack launch (plus one compaction launch): e.g. the keys and the values of a layer, each
+ * with its own window, outputs and histogram.  `jobs` is host memory, read before the call
+ * returns.  Every job's outputs are exactly what adacode_pack_tiles would write for it.
+ * Replaces: the pair of compress_tiled_tensor calls per flushed block in
+ *   float11Layer._compress_span (float_cache_utils.py:993-1011), i.e. two passes of
+ *   CompressorBitMap.compress per 128 tokens, by one launch per prefill span.
+ * The scratch must hold adacode_pack_workspace_bytes(total tiles of all jobs, seq_tile*D);
+ * the elements of all jobs together must stay below 2**31.
+ */
+int adacode_pack_jobs(const adacode_pack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D, int nbits,
+                      void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
  * Maximum size of the library-owned scratch used by adacode_pack_tiles_static, in bytes.
  * A call fits when adacode_pack_workspace_bytes(n_tiles, tile_elems) is not larger (roughly
  * 4 Mi bf16 elements per call, e.g. thirty-two 128-token blocks of an [8, 128]-shaped head set).
@@ -167,6 +202,36 @@ typedef struct adacode_segment {
 int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments, int B, int H,
                             int seq_tile, int D, void *dst_bf16, int64_t dstride_b, int64_t dstride_h,
                             int64_t dstride_s, int32_t *status, void *stream);
+
+/*
+ * Testing aid for the failure path of the pipelined kernels; not needed in normal use.
+ * Every on-chip wait of those kernels is bounded: after `polls` failed polls (0 restores the
+ * default, 2**22) the waiter ORs ADACODE_STATUS_TIMEOUT into *status and carries on, so a launch
+ * always ends.  With withhold_unit >= 0 the next adacode_unpack_* launches never signal that unit
+ * (counted per CTA, CTA 0 only) as loaded and give it nothing to do, so that its wait runs out:
+ * the call still returns, the status word says TIMEOUT, no memory outside the call's buffers is
+ * touched.  -1 switches this off.  Process-wide, not thread-safe.
+ * The reference implementation has no counterpart (its kernels never wait on one another).
+ */
+int adacode_debug_set_wait_limit(unsigned int polls, int withhold_unit);
+
+/* One destination of a multi-tensor unpack launch (adacode_unpack_jobs). */
+typedef struct adacode_unpack_job {
+    const adacode_segment *segments_dev; /* device array, n_segments records */
+    int32_t n_segments;
+    int32_t reserved;
+    void *dst_bf16;
+    int64_t dstride_b, dstride_h, dstride_s;
+} adacode_unpack_job;
+
+/*
+ * adacode_unpack_segments for up to adacode_max_jobs() destinations of one shape in one launch
+ * (the keys and the values of a layer).  `jobs` is host memory, read before the call returns.
+ * Replaces: the two _materialize_prefix_segmented_tiled passes (keys, values) of
+ *   float11Layer.materialize_dense (float_cache_utils.py:1245-1290).
+ */
+int adacode_unpack_jobs(const adacode_unpack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D,
+                        int32_t *status, void *stream);
 
 /*
  * hist256 += 256-bin histogram of the exponent field of src[B][H][S][D].

@@ -1,22 +1,31 @@
 """Kernel-level timing of pack and unpack on one GPU, for profiling and tuning.
 
-``python -m adacode_b200.microbench --shape 16,8,8192,128 --nbits 4 --right 131 --iters 5``
+``python microbench.py --shape 16,8,8192,128 --nbits 4 --right 131 --iters 5``
 
 Packs a seeded synthetic K tensor [B, H, S, D] (all S/128 blocks in one launch) and unpacks it
 again, timing each kernel with CUDA events on the launching stream (several launches back to
 back per sample, so that host launch latency is not counted), and prints one line per
 kernel with the algorithmic HBM bytes (2 read + 1 + nbits/8 + p written per element for pack,
-the mirror image for unpack, p = escape fraction) divided by the time.  Inputs are larger
-than L2 when the shape is; nothing is copied from or to the host inside the timed region.
+the mirror image for unpack, p = escape fraction) divided by the time.  ``--pair`` times a K and a
+V tensor of that shape going through ONE launch (``adacode_pack_jobs`` / ``adacode_unpack_jobs``).
+Inputs are larger than L2 when the shape is; nothing is copied from or to the host inside the
+timed region.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import os
+import sys
 
 import torch
 
-from . import _lib, codec
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from adacode_b200 import _lib, codec  # noqa: E402
 
 
 def synthetic_keys(shape, seed: int = 0, device='cuda') -> torch.Tensor:
@@ -61,7 +70,7 @@ def attention_main(args) -> None:
     2 bytes and lets the attention kernel read 2 bytes again."""
     import torch.nn.functional as F
 
-    from . import attention
+    from adacode_b200 import attention
     shape = tuple(int(v) for v in args.shape.split(','))
     B, H, S, D = shape
     Hq = args.attention
@@ -103,6 +112,61 @@ def attention_main(args) -> None:
         }))
 
 
+def pair_main(args) -> None:
+    """K and V of one shape through one pack launch and one unpack launch."""
+    shape = tuple(int(v) for v in args.shape.split(','))
+    B, H, S, D = shape
+    dev = torch.device('cuda', 0)
+    T = args.seq_tile
+    n_blocks = S // T
+    xs = [synthetic_keys(shape, seed=i, device=dev) for i in range(2)]
+    n = xs[0].numel()
+    L = _lib.lib()
+    sc = codec._scratch_for(dev)
+    ws = sc.workspace_for(2 * B * H * n_blocks, T * D)
+    chunks = [codec.pack_blocks(x, args.right, args.nbits, T)[0] for x in xs]
+    p = sum(c.n_escapes for c in chunks) / (2 * n)
+    jobs = (_lib.PackJob * 2)()
+    keep = []
+    for jb, x, c in zip(jobs, xs, chunks):
+        meta = torch.zeros(n_blocks + 2, dtype=torch.int64, device=dev)
+        esc = torch.empty(max(c.n_escapes, 16), dtype=torch.uint8, device=dev)
+        hist = torch.zeros(256, dtype=torch.int32, device=dev)
+        keep += [meta, esc, hist]
+        sb, sh, ss, _ = x.stride()
+        jb.src_bf16, jb.stride_b, jb.stride_h, jb.stride_s = x.data_ptr(), sb, sh, ss
+        jb.n_blocks, jb.right = n_blocks, args.right
+        jb.sign_mant, jb.codes, jb.escapes = c.sign_mant.data_ptr(), c.codes.data_ptr(), esc.data_ptr()
+        jb.escapes_capacity = esc.numel()
+        jb.tile_base, jb.seg_escape_offsets = c.tile_base.data_ptr(), meta.data_ptr()
+        jb.hist256 = 0 if args.no_hist else hist.data_ptr()
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    outs = [torch.empty_like(x) for x in xs]
+    tables = [codec.build_segment_table(c.segments(), None, dev) for c in chunks]
+    todo = [(c.segments(), o, t) for c, o, t in zip(chunks, outs, tables)]
+
+    def pack():
+        _lib.check(L.adacode_pack_jobs(ctypes.addressof(jobs), 2, B, H, T, D, args.nbits, ws.data_ptr(), ws.numel(),
+                                       status.data_ptr(), stream), 'adacode_pack_jobs')
+
+    def unpack():
+        codec.unpack_segments_multi(todo)
+
+    t_pack = _time(pack, args.iters, args.warmup)
+    t_unpack = _time(unpack, args.iters, args.warmup)
+    assert int(status[0].item()) == 0
+    for x, o in zip(xs, outs):
+        assert torch.equal(o.view(torch.int16), x.view(torch.int16)), 'round trip is not bit-exact'
+    alg = 2 * n * (3.0 + args.nbits / 8.0 + p)
+    for name, t in (('pack_pair', t_pack), ('unpack_pair', t_unpack)):
+        print(json.dumps({
+            'kernel': name, 'shape': list(shape), 'nbits': args.nbits, 'right': args.right,
+            'escape_fraction': round(p, 5), 'us': round(t * 1e6, 1),
+            'algorithmic_GBps': round(alg / t / 1e9, 1), 'bf16_equiv_GBps': round(4 * n / t / 1e9, 1),
+        }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument('--shape', default='16,8,8192,128')
@@ -112,12 +176,15 @@ def main() -> None:
     ap.add_argument('--iters', type=int, default=5)
     ap.add_argument('--warmup', type=int, default=2)
     ap.add_argument('--no-hist', action='store_true')
+    ap.add_argument('--pair', action='store_true', help='a K and a V tensor per launch (job-table entry points)')
     ap.add_argument('--attention', type=int, default=0, metavar='HQ',
                     help='time decode attention with HQ query heads instead: fused (packed planes) '
                          'against unpack + torch SDPA over dense K/V')
     args = ap.parse_args()
     if args.attention:
         return attention_main(args)
+    if args.pair:
+        return pair_main(args)
     shape = tuple(int(v) for v in args.shape.split(','))
     B, H, S, D = shape
     dev = torch.device('cuda', 0)

@@ -76,6 +76,12 @@ def unpack_segments(segments, dst, seq_offsets=None, table=None):
         run = off + T
 
 
+def unpack_segments_multi(jobs):
+    for segments, dst, table in jobs:
+        if segments:
+            unpack_segments(segments, dst, table=table)
+
+
 def exponent_hist(x, hist_out=None):
     h = torch.from_numpy(O.exponent_hist(x.to(torch.bfloat16).contiguous())).to(torch.int32)
     if hist_out is not None:

@@ -205,3 +205,33 @@ def test_calibration_producer_feeds_the_consumer(cuda_device, tmp_path):
         assert (rights[l][1], nbits[l][1]) == tuple(O.calibrate_coo(vh))
     whole = extract_exp_freq(cache)                      # no split
     assert whole[0]['keys'] == O.exponent_hist(tensors[1][0][0]).tolist()
+
+
+def test_runner_writes_reference_shaped_records(cuda_device, tmp_path, monkeypatch):
+    """``main_lossless_comp`` with ``--use_synthetic_data --random_init``: the calibration JSON is
+    produced on the spot, the float11 run generates the token ids of the DynamicCache run, and the
+    per-batch record carries the reference's keys (main_lossless_comp.py:342-458)."""
+    import json
+    from adacode_b200 import main_lossless_comp as runner
+    monkeypatch.chdir(tmp_path)
+    common = ['--model_config_name', 'llama_3p1_8B_config', '--use_synthetic_data', '--synthetic_seq_length', '300',
+              '--batch_size', '2', '--num_seqence', '2', '--max_new_tokens', '140', '--min_new_tokens', '140',
+              '--random_init', '--random_init_layers', '2']
+    recs = {}
+    for impl, extra in (('dynamic', []), ('float11', ['--float11_need_adjust', '--float11_update_steps', '128'])):
+        args = runner.get_parse().parse_args(common + ['--kv_cache_impl', impl, '--output_path', f'{impl}.json'] + extra)
+        out = runner.run(args)
+        on_disk = json.loads((tmp_path / f'{impl}.json').read_text())
+        assert on_disk == out and len(out['synthetic']) == 1
+        recs[impl] = out['synthetic'][0]
+    assert (tmp_path / 'model_configs' / 'kv_test_Meta-Llama-3.1-8B-Instruct_exp.json').exists()
+    f11, dyn = recs['float11'], recs['dynamic']
+    assert f11['generated_output_head_32'] == dyn['generated_output_head_32']
+    for key in ('dataset', 'sample_start_idx', 'batch_size', 'cache_mode', 'input_shape', 'total_input_tokens',
+                'generate_time', 'total_new_tokens', 'tokens_per_second', 'kv_compressed_memory', 'kv_original_memory',
+                'float11_layout', 'float11_need_adjust', 'float11_update_steps', 'cuda_peak_allocated_gib'):
+        assert key in f11, key
+    assert f11['input_shape'] == [2, 300] and f11['total_new_tokens'] == 2 * 140
+    assert 0.6 < f11['kv_compressed_memory'] / f11['kv_original_memory'] < 1.0
+    with pytest.raises(NotImplementedError):
+        runner.run(runner.get_parse().parse_args(common + ['--kv_cache_impl', 'nvcomp_ans']))

@@ -264,3 +264,124 @@ def test_randomised_shapes_windows_and_escape_rates(cuda_device):
             codec.unpack_chunk(vc, back)
             assert np.array_equal(_u16(back), _u16(x_cpu)), f'case {case}: pair unpack'
     codec.check_device_status(cuda_device)
+
+
+def test_pack_jobs_three_tensors_one_launch(cuda_device):
+    """``adacode_pack_jobs`` through the raw C ABI: three tensors of one shape family (different
+    block counts, windows, one without a histogram) in one launch equal three ordinary packs."""
+    import ctypes
+    from adacode_b200 import _lib, codec
+    L = _lib.lib()
+    B, H, D, nbits = 2, 3, 128, 3
+    specs = [(384, 129, True), (128, 127, False), (256, 131, True)]
+    xs = [synth.inject_escapes(synth.kv_tensor((B, H, S, D), seed=70 + i, key_offset=bool(i & 1)), seed=80 + i,
+                               left=r - 7, right=r).to(cuda_device) for i, (S, r, _) in enumerate(specs)]
+    jobs = (_lib.PackJob * len(specs))()
+    outs = []
+    n_tiles = 0
+    for jb, x, (S, right, want_hist) in zip(jobs, xs, specs):
+        nb = S // 128
+        n = x.numel()
+        o = {'sm': torch.zeros(n, dtype=torch.uint8, device=cuda_device),
+             'codes': torch.zeros(n * nbits // 8, dtype=torch.uint8, device=cuda_device),
+             'esc': torch.zeros(n, dtype=torch.uint8, device=cuda_device),
+             'base': torch.zeros(B * H * nb, dtype=torch.int32, device=cuda_device),
+             'off': torch.zeros(nb + 1, dtype=torch.int64, device=cuda_device),
+             'hist': torch.zeros(256, dtype=torch.int32, device=cuda_device) if want_hist else None}
+        outs.append(o)
+        sb, sh, ss, _ = x.stride()
+        jb.src_bf16, jb.stride_b, jb.stride_h, jb.stride_s = x.data_ptr(), sb, sh, ss
+        jb.n_blocks, jb.right = nb, right
+        jb.sign_mant, jb.codes, jb.escapes = o['sm'].data_ptr(), o['codes'].data_ptr(), o['esc'].data_ptr()
+        jb.escapes_capacity = n
+        jb.tile_base, jb.seg_escape_offsets = o['base'].data_ptr(), o['off'].data_ptr()
+        jb.hist256 = o['hist'].data_ptr() if want_hist else 0
+        n_tiles += B * H * nb
+    ws = torch.zeros(L.adacode_pack_workspace_bytes(n_tiles, 128 * D), dtype=torch.uint8, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    for _ in range(2):                                   # the scratch is left ready for the next call
+        for o in outs:
+            if o['hist'] is not None:
+                o['hist'].zero_()
+        rc = L.adacode_pack_jobs(ctypes.addressof(jobs), len(specs), B, H, 128, D, nbits, ws.data_ptr(), ws.numel(),
+                                 status.data_ptr(), torch.cuda.current_stream(cuda_device).cuda_stream)
+        assert rc == 0, L.adacode_strerror(rc)
+        torch.cuda.synchronize(cuda_device)
+        assert int(status.item()) == 0
+        for o, x, (S, right, want_hist) in zip(outs, xs, specs):
+            ref, ref_hist = codec.pack_blocks(x, right, nbits, 128, need_hist=True)
+            assert o['off'].cpu().tolist() == ref.seg_offsets
+            total = ref.seg_offsets[-1]
+            assert torch.equal(o['sm'], ref.sign_mant.reshape(-1)) and torch.equal(o['codes'], ref.codes.reshape(-1))
+            assert torch.equal(o['esc'][:total], ref.escapes) and torch.equal(o['base'], ref.tile_base.reshape(-1))
+            if want_hist:
+                assert torch.equal(o['hist'], ref_hist)
+            _check_chunk_against_oracle(ref, ref_hist, x.cpu(), right, nbits, 128)
+    assert L.adacode_pack_jobs(ctypes.addressof(jobs), L.adacode_max_jobs() + 1, B, H, 128, D, nbits, ws.data_ptr(),
+                               ws.numel(), status.data_ptr(), 0) == _lib.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize('D', [128, 96, 512])
+def test_unpack_jobs_and_token_major_destination(cuda_device, D):
+    """Keys and values unpacked by one launch (``adacode_unpack_jobs``), the keys into a
+    destination whose token rows are not adjacent ([B, S, H, D] memory viewed as [B, H, S, D])."""
+    from adacode_b200 import codec
+    B, H, S = 2, 3, 384
+    k_cpu = synth.kv_tensor((B, H, S, D), seed=41, key_offset=True)
+    v_cpu = synth.inject_escapes(synth.kv_tensor((B, H, S, D), seed=42), seed=43, left=121, right=128, p_window=0.2)
+    kc, _ = codec.pack_blocks(k_cpu.to(cuda_device), 129, 3, 128)
+    vc, _ = codec.pack_blocks(v_cpu.to(cuda_device), 128, 3, 128)
+    k_dst = torch.zeros((B, S, H, D), dtype=torch.bfloat16, device=cuda_device).transpose(1, 2)
+    v_dst = torch.zeros((B, H, S + 128, D), dtype=torch.bfloat16, device=cuda_device)
+    codec.unpack_segments_multi([(kc.segments(), k_dst, None), (vc.segments(), v_dst, None)])
+    assert np.array_equal(_u16(k_dst), _u16(k_cpu))
+    assert np.array_equal(_u16(v_dst[:, :, :S]), _u16(v_cpu))
+    assert int(v_dst[:, :, S:].abs().sum()) == 0
+    one = torch.zeros((B, S, H, D), dtype=torch.bfloat16, device=cuda_device).transpose(1, 2)
+    codec.unpack_chunk(vc, one)
+    assert np.array_equal(_u16(one), _u16(v_cpu))
+    codec.check_device_status(cuda_device)
+
+
+def test_status_word_misaligned_record(cuda_device):
+    """A segment record whose plane pointer is off by one byte (inside a valid buffer) is never
+    handed to a bulk copy: the call returns, the tile is skipped, the status word says so."""
+    from adacode_b200 import _lib, codec
+    x_cpu = synth.kv_tensor((1, 2, 256, 128), seed=51)
+    chunk, _ = codec.pack_blocks(x_cpu.to(cuda_device), 129, 3, 128)
+    segs = chunk.segments()
+    table = codec.build_segment_table(segs, None, cuda_device)
+    rec = table.view(torch.int64)
+    rec[7] += 1                                   # sign_mant pointer of segment 1 (7 int64 words per record)
+    out = torch.zeros_like(x_cpu, device=cuda_device)
+    codec.unpack_segments(segs, out, table=table)
+    with pytest.raises(_lib.AdacodeError, match='not 16-byte aligned'):
+        codec.check_device_status(cuda_device)
+    assert np.array_equal(_u16(out[:, :, :128]), _u16(x_cpu[:, :, :128].contiguous()))   # segment 0 is untouched by it
+    assert int(out[:, :, 128:].abs().sum()) == 0                                          # segment 1 was skipped
+    codec.check_device_status(cuda_device)        # the word was cleared; the context is usable
+    codec.unpack_segments(segs, out)
+    assert np.array_equal(_u16(out), _u16(x_cpu))
+
+
+def test_status_word_timeout_of_a_bounded_wait(cuda_device):
+    """The bounded on-chip wait: with the poll limit lowered and one unit never signalled as
+    loaded (``adacode_debug_set_wait_limit``) the launch still ends, reports TIMEOUT and leaves the
+    context usable.  Nothing faults or hangs: the withheld unit has nothing to do."""
+    from adacode_b200 import _lib, codec
+    L = _lib.lib()
+    x_cpu = synth.kv_tensor((1, 2, 128, 128), seed=52)
+    chunk, _ = codec.pack_blocks(x_cpu.to(cuda_device), 129, 3, 128)
+    out = torch.zeros_like(x_cpu, device=cuda_device)
+    try:
+        L.adacode_debug_set_wait_limit(20000, 0)
+        codec.unpack_chunk(chunk, out)
+        torch.cuda.synchronize(cuda_device)
+    finally:
+        L.adacode_debug_set_wait_limit(0, -1)
+    with pytest.raises(_lib.AdacodeError, match='bounded on-chip wait'):
+        codec.check_device_status(cuda_device)
+    out.zero_()
+    codec.unpack_chunk(chunk, out)
+    assert np.array_equal(_u16(out), _u16(x_cpu))
+    codec.check_device_status(cuda_device)
