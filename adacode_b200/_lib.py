@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     'adacode_choose_params', 'adacode_choose_params_host', 'adacode_calibrate_host', 'adacode_pack_tiles_static',
     'adacode_decode_attn_workspace_bytes', 'adacode_decode_attn', 'adacode_copy_to_host',
     'adacode_pack_jobs', 'adacode_unpack_jobs', 'adacode_max_jobs', 'adacode_debug_set_wait_limit',
+    'adacode_flat_block_elems', 'adacode_unpack_flat',
 )
 
 
@@ -113,6 +114,10 @@ def lib() -> ctypes.CDLL:
     L.adacode_copy_to_host.restype = i32
     L.adacode_copy_to_host.argtypes = [vp, vp, sz, vp]
     L.adacode_max_jobs.restype = i32
+    L.adacode_flat_block_elems.restype = i32
+    L.adacode_flat_block_elems.argtypes = [i32]
+    L.adacode_unpack_flat.restype = i32
+    L.adacode_unpack_flat.argtypes = [vp, vp, vp, i64, vp, i64, i32, i32, vp, vp, vp]
     L.adacode_debug_set_wait_limit.restype = i32
     L.adacode_debug_set_wait_limit.argtypes = [ctypes.c_uint, i32]
     L.adacode_pack_jobs.restype = i32

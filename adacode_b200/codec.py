@@ -527,6 +527,27 @@ def _segment_dtype():
     return _SEGMENT_DTYPE
 
 
+def _check_segment_buffers(seg) -> None:
+    """A segment record carries raw pointers: refuse on the host what would fault on the device."""
+    B, H, T, D = (int(v) for v in seg.original_shape)
+    n = B * H * T * D
+    nbits = int(seg.nbits)
+    if nbits not in _SUPPORTED_TILE_NBITS:
+        raise ValueError(f'Tiled compressed path supports nbits in {_SUPPORTED_TILE_NBITS}, got {nbits}')
+    if seg.sign_mass_data.dtype != torch.uint8 or seg.sign_mass_data.numel() < n:
+        raise ValueError(f'segment sign_mass_data must hold {n} uint8 values, got {seg.sign_mass_data.numel()}')
+    if seg.exp_data.dtype != torch.uint8 or seg.exp_data.numel() < n * nbits // 8:
+        raise ValueError(f'segment exp_data must hold {n * nbits // 8} uint8 values, got {seg.exp_data.numel()}')
+    base = seg.tile_invalid_base
+    if base.dtype != torch.int32 or base.numel() < B * H or not base.is_contiguous():
+        raise ValueError(f'segment tile_invalid_base must be {B * H} contiguous int32 values, got '
+                         f'{base.numel()} of {base.dtype}')
+    if n and (seg.sign_mass_data.data_ptr() % 16 or seg.exp_data.data_ptr() % 16):
+        raise ValueError('segment planes must start on 16-byte boundaries')
+    if seg.invalid_exp.numel() and seg.invalid_exp.dtype != torch.uint8:
+        raise ValueError('segment invalid_exp must be uint8')
+
+
 def build_segment_table(segments: Sequence, seq_offsets: Optional[Sequence[int]] = None,
                         device=None) -> torch.Tensor:
     """Device array of ``adacode_segment`` records (as uint8) for ``unpack_segments``.
@@ -565,6 +586,7 @@ def build_segment_table(segments: Sequence, seq_offsets: Optional[Sequence[int]]
         else:
             k = i + 1
             rows = table[i:k]
+            _check_segment_buffers(seg)
             rows['sign_mant'] = seg.sign_mass_data.data_ptr()
             rows['codes'] = seg.exp_data.data_ptr()
             rows['escapes'] = seg.invalid_exp.data_ptr() if seg.invalid_exp.numel() else 0

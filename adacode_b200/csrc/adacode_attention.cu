@@ -791,6 +791,7 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         UnpackPipeArgs u;
         u.sign_mant = nullptr, u.codes = nullptr, u.escapes = nullptr, u.escapes_len = 0;
         u.tile_base = nullptr, u.seg_off = nullptr, u.left = 0, u.nbits = 0;
+        u.tb_stride = 1, u.tb_before = 0;
         u.H = Hkv, u.BH = B * Hkv, u.seq_tile = kTileTokens, u.D = D, u.tile_elems = kTileTokens * D;
         u.n_tiles = (long long)n_segments * B * Hkv;
         u.dst = nullptr, u.db = 0, u.dh = 0, u.ds = 0, u.status = status;

@@ -992,6 +992,7 @@ int adacode_unpack_tiles(const uint8_t *sign_mant, const uint8_t *codes, const u
         UnpackPipeArgs pa;
         pa.sign_mant = sign_mant, pa.codes = codes, pa.escapes = escapes, pa.escapes_len = escapes_len;
         pa.tile_base = tile_base, pa.seg_off = seg_escape_offsets, pa.left = left, pa.nbits = nbits;
+        pa.tb_stride = 1, pa.tb_before = 0;
         pa.seg = nullptr;
         pa.H = H, pa.BH = B * H, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = seq_tile * D;
         pa.n_tiles = n_tiles, pa.dst = (uint16_t *)dst_bf16;
@@ -1029,6 +1030,7 @@ int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments,
         UnpackPipeArgs pa;
         pa.sign_mant = nullptr, pa.codes = nullptr, pa.escapes = nullptr, pa.escapes_len = 0;
         pa.tile_base = nullptr, pa.seg_off = nullptr, pa.left = 0, pa.nbits = 0;
+        pa.tb_stride = 1, pa.tb_before = 0;
         pa.seg = segments_dev;
         pa.H = H, pa.BH = B * H, pa.seq_tile = seq_tile, pa.D = D, pa.tile_elems = seq_tile * D;
         pa.n_tiles = n_tiles, pa.dst = (uint16_t *)dst_bf16;
@@ -1039,6 +1041,54 @@ int adacode_unpack_segments(const adacode_segment *segments_dev, int n_segments,
     if (D % 16 == 0) k_unpack_segments<16><<<grid, kThreads, 0, st>>>(u, segments_dev, n_tiles);
     else k_unpack_segments<8><<<grid, kThreads, 0, st>>>(u, segments_dev, n_tiles);
     ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
+}
+
+int adacode_flat_block_elems(int nbits) {
+    static const int gaps[4] = {8, 4, 8, 2};
+    return (nbits < 1 || nbits > 4) ? 0 : 128 * gaps[nbits - 1];
+}
+
+int adacode_unpack_flat(const uint8_t *sign_mant, const uint8_t *codes, const uint8_t *escapes, int64_t escapes_len,
+                        const int32_t *block_base, int64_t n_elems, int left, int nbits, void *dst_bf16,
+                        int32_t *status, void *stream) {
+    const int be = adacode_flat_block_elems(nbits);
+    if (be == 0 || n_elems < 0 || n_elems % be != 0 || !status) return ADACODE_ERR_INVALID_ARG;
+    if (n_elems == 0) return ADACODE_OK;
+    if (n_elems >= (1ll << 31)) return ADACODE_ERR_TOO_LARGE;
+    if (!sign_mant || !codes || !block_base || !dst_bf16) return ADACODE_ERR_INVALID_ARG;
+    if ((((uintptr_t)sign_mant | (uintptr_t)codes | (uintptr_t)dst_bf16) & 15) != 0) return ADACODE_ERR_INVALID_ARG;
+    if (!pipeline_enabled()) return ADACODE_ERR_INVALID_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the bulk of the tensor as 128 x 128 tiles whose escape base is every (16384 / be)-th block base,
+    // the rest (fewer than 16384 elements) block by block
+    const int64_t big = 128 * 128;
+    const int64_t n_big = n_elems / big;
+    const int64_t n_main = n_big * big;
+    UnpackPipeArgs pa;
+    memset(&pa, 0, sizeof(pa));
+    pa.escapes = escapes, pa.escapes_len = escapes_len, pa.seg_off = nullptr, pa.left = left, pa.nbits = nbits;
+    pa.seg = nullptr, pa.status = status;
+    if (n_big > 0) {
+        pa.sign_mant = sign_mant, pa.codes = codes, pa.tile_base = block_base;
+        pa.tb_stride = (int)(big / be), pa.tb_before = 0;
+        pa.H = (int)n_big, pa.BH = (int)n_big, pa.seq_tile = 128, pa.D = 128, pa.tile_elems = (int)big;
+        pa.n_tiles = n_big, pa.dst = (uint16_t *)dst_bf16;
+        pa.db = 0, pa.dh = big, pa.ds = 128;
+        int rc = launch_unpack_pipe(pa, st);
+        if (rc != ADACODE_OK) return rc;
+    }
+    const int64_t n_rest = (n_elems - n_main) / be;
+    if (n_rest > 0) {
+        pa.sign_mant = sign_mant + n_main, pa.codes = codes + n_main * nbits / 8;
+        pa.tile_base = block_base + n_main / be;
+        pa.tb_stride = 1, pa.tb_before = n_main > 0 ? 1 : 0;
+        pa.H = (int)n_rest, pa.BH = (int)n_rest, pa.seq_tile = be / 32, pa.D = 32, pa.tile_elems = be;
+        pa.n_tiles = n_rest, pa.dst = (uint16_t *)dst_bf16 + n_main;
+        pa.db = 0, pa.dh = be, pa.ds = 32;
+        int rc = launch_unpack_pipe(pa, st);
+        if (rc != ADACODE_OK) return rc;
+    }
     return ADACODE_OK;
 }
 

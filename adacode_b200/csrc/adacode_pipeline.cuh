@@ -189,6 +189,8 @@ struct UnpackPipeArgs {
     const int32_t *tile_base;
     const int64_t *seg_off;
     int left, nbits;
+    int tb_stride;            // tile t's inclusive base is tile_base[(t + 1) * tb_stride - 1] (1: one entry per tile)
+    int tb_before;            // tile_base[-1] exists and holds the escapes before tile 0
     // table form
     const adacode_segment *seg;
     // common
@@ -231,9 +233,10 @@ __device__ __forceinline__ TileSrc resolve_tile(const UnpackPipeArgs &a, long lo
         t.codes = a.codes + tile * (a.tile_elems * a.nbits / 8);
         t.esc = a.escapes, t.esc_len = a.escapes_len;
         const long long seg_start = a.seg_off ? a.seg_off[blk] : 0;
-        const int prev = bh > 0 ? a.tile_base[tile - 1] : 0;
+        const long long ts = a.tb_stride > 1 ? a.tb_stride : 1;
+        const int prev = (bh > 0 || a.tb_before) ? a.tile_base[tile * ts - 1] : 0;
         t.esc_start = seg_start + prev;
-        t.esc_cnt = a.tile_base[tile] - prev;
+        t.esc_cnt = a.tile_base[tile * ts + ts - 1] - prev;
         t.dst = base + blk * a.seq_tile * a.ds;
     }
     return t;

@@ -36,7 +36,8 @@ from transformers.cache_utils import DynamicLayer
 from . import codec
 from .codec import SegmentRef, TiledCompressedTensor
 
-_SUPPORTED_LAYOUTS = ('segmented_tiled',)
+_SUPPORTED_LAYOUTS = ('segmented_tiled', 'legacy', 'tiled')
+_LEGACY_BLOCK_GAPS = (8, 4, 8, 2)      # escape-base blocks of the flat layout: 128 x gap elements
 
 
 def _segmented_state(segment_states: list) -> Optional[dict]:
@@ -153,8 +154,7 @@ class float11Layer(DynamicLayer):
     ):
         super().__init__()
         if layout not in _SUPPORTED_LAYOUTS:
-            raise NotImplementedError(
-                f"layout={layout!r}: this implementation covers the 'segmented_tiled' layout only")
+            raise ValueError(f'layout={layout!r}: expected one of {_SUPPORTED_LAYOUTS}')
         if dense_workspace not in ('shared', 'layer'):
             raise ValueError("dense_workspace must be 'shared' or 'layer'")
         self.residual_length = residual_length
@@ -303,6 +303,17 @@ class float11Layer(DynamicLayer):
         if (int(old_values[0]), int(old_values[1])) != (int(new_values[0]), int(new_values[1])):
             self.values_update_times += 1
 
+    def adjust_compressor(self, keys_exp_count, values_exp_count) -> None:
+        """'legacy' / 'tiled' layouts: the windows proposed by the histograms of the blocks packed on
+        an adjust step wait in ``new_*`` until the next adjust step adopts them; nothing already packed
+        changes (reference: :664-669; there the call runs on a thread pool and is joined at the next
+        adjust step, here it runs at once)."""
+        new_keys = codec.analysis_best_bits(keys_exp_count)
+        new_values = codec.analysis_best_bits(values_exp_count)
+        self._record_adjust_proposal(new_keys, new_values)
+        self.new_keys_right, self.new_keys_nbits = int(new_keys[0]), int(new_keys[1])
+        self.new_values_right, self.new_values_nbits = int(new_values[0]), int(new_values[1])
+
     def has_pending_adjust_recompress(self) -> bool:
         return self._pending_adjust_recompress_start_segment is not None
 
@@ -363,18 +374,42 @@ class float11Layer(DynamicLayer):
             raise ValueError(
                 'Tiled compressed path currently requires seq_tile_size == seq_len per compressed block, '
                 f'got seq_tile_size={self.seq_tile_size}, seq_len={self.block_size}')
-        # keys and values are launched back to back and share one read of their escape totals, status
-        # words and histograms; the escape buffers are sized from what this layer's last span needed
-        nk, nv = key_states.numel(), value_states.numel()
-        caps = tuple(None if f is None else int(n * f * 1.25) + 4096 for n, f in zip((nk, nv), self._escape_fraction))
-        k_chunk, v_chunk, k_hist, v_hist, kh_host, vh_host = codec.pack_pair(
-            key_states, value_states, (self.keys_right, self.keys_nbits), (self.values_right, self.values_nbits),
-            self.seq_tile_size, need_hist=need_adjust, capacities=caps)
-        self._escape_fraction = (k_chunk.n_escapes / max(nk, 1), v_chunk.n_escapes / max(nv, 1))
+        if self.layout == 'tiled':
+            # one unified state per tensor: a block of another code length cannot join it
+            # (reference: _append_tiled_prefix_state, :277-283)
+            for segs, nbits in ((self._key_segments, self.keys_nbits), (self._value_segments, self.values_nbits)):
+                if segs and int(segs[0].nbits) != int(nbits):
+                    raise ValueError('Tiled prefix append requires matching nbits, '
+                                     f'got existing={int(segs[0].nbits)}, new={int(nbits)}')
+        # keys and values go through one launch (two when their code lengths differ) and share one read
+        # of their escape totals, status words and histograms; the escape buffers are sized from what
+        # this layer's last span needed.  A launch covers fewer than 2**31 elements: longer spans are
+        # packed in several launches, block range by block range.
+        B, H, S, D = key_states.shape
+        per_block = max(int(B * H * self.seq_tile_size * max(D, value_states.shape[-1])), 1)
+        blocks_per_call = max(1, (2 ** 31 - 1) // (2 * per_block))
+        total_blocks = S // self.seq_tile_size
+        k_hist = v_hist = kh_host = vh_host = None
+        for b_lo in range(0, total_blocks, blocks_per_call):
+            t_lo = b_lo * self.seq_tile_size
+            t_hi = min(total_blocks, b_lo + blocks_per_call) * self.seq_tile_size
+            ks, vs = key_states[:, :, t_lo:t_hi], value_states[:, :, t_lo:t_hi]
+            nk, nv = ks.numel(), vs.numel()
+            caps = tuple(None if f is None else int(n * f * 1.25) + 4096 for n, f in zip((nk, nv), self._escape_fraction))
+            k_chunk, v_chunk, kh, vh, kh_h, vh_h = codec.pack_pair(
+                ks, vs, (self.keys_right, self.keys_nbits), (self.values_right, self.values_nbits),
+                self.seq_tile_size, need_hist=need_adjust, capacities=caps)
+            self._escape_fraction = (k_chunk.n_escapes / max(nk, 1), v_chunk.n_escapes / max(nv, 1))
+            if need_adjust:
+                if k_hist is None:
+                    k_hist, v_hist, kh_host, vh_host = kh, vh, kh_h, vh_h
+                else:
+                    k_hist, v_hist = k_hist + kh, v_hist + vh
+                    kh_host, vh_host = kh_host + kh_h, vh_host + vh_h
+            self._key_segments.extend(k_chunk.segments())
+            self._value_segments.extend(v_chunk.segments())
         self._host_hists = (k_hist, kh_host, v_hist, vh_host) if need_adjust else None
-        self._key_segments.extend(k_chunk.segments())
-        self._value_segments.extend(v_chunk.segments())
-        n_blocks = k_chunk.n_blocks
+        n_blocks = total_blocks
         tokens = n_blocks * self.seq_tile_size
         self._compressed_prefix_seq_len += tokens
         self._compressed_block_flushes += n_blocks
@@ -442,7 +477,7 @@ class float11Layer(DynamicLayer):
         if delay_segmented_block:
             k_hist, v_hist = self._stage_dense_block(collect_adjust_hist)
             return k_hist, v_hist, False
-        start_segment = len(self._key_segments) if need_adjust else None
+        start_segment = len(self._key_segments) if need_adjust and self.layout == 'segmented_tiled' else None
         k_hist, v_hist, flushed = self._flush_full_blocks_from_residual(need_adjust)
         if start_segment is not None and k_hist is not None:
             self.mark_adjust_recompress_start(start_segment)
@@ -635,8 +670,10 @@ class float11Layer(DynamicLayer):
             if res_k is None:
                 return self._empty_states(), self._empty_states()
             return res_k, res_v
-        if self._materialized_prefix_seq_len == int(self._compressed_prefix_seq_len):
-            self.materialize_cache_hits += 1     # no block was packed since the last call (reference: :1250-1256)
+        if self._materialized_prefix_seq_len == int(self._compressed_prefix_seq_len) and self.layout != 'tiled':
+            # no block was packed since the last call (reference: :1250-1256; its 'tiled' layout has no
+            # cached prefix and never counts a hit)
+            self.materialize_cache_hits += 1
         self._materialized_prefix_seq_len = int(self._compressed_prefix_seq_len)
         keys, values = self._materialize_into_workspace()
         self.materialize_time += time.perf_counter() - begin
@@ -664,8 +701,14 @@ class float11Layer(DynamicLayer):
     # ------------------------------------------------------------------ introspection
     def get_cache_view(self) -> dict:
         """reference: :1331-1361."""
-        key_meta = _segmented_state([s.export_decode_view() for s in self._key_segments])
-        value_meta = _segmented_state([s.export_decode_view() for s in self._value_segments])
+        if self.layout == 'segmented_tiled':
+            key_meta = _segmented_state([s.export_decode_view() for s in self._key_segments])
+            value_meta = _segmented_state([s.export_decode_view() for s in self._value_segments])
+        elif self.layout == 'tiled':
+            key_meta = self._unified_tiled_state(self._key_segments)
+            value_meta = self._unified_tiled_state(self._value_segments)
+        else:
+            key_meta = value_meta = None           # the flat layout publishes no prefix metadata (reference: :1052-1066)
         res_k, res_v = self._active_residual_tensors()
         return {
             'layout': self.layout,
@@ -682,6 +725,80 @@ class float11Layer(DynamicLayer):
             '_float11_layer': self,
         }
 
+    # per-block states in the reference's own schemas, for consumers written against them
+    @property
+    def _compressed_prefix_key_blocks(self) -> list:
+        return [self._legacy_block_state(s) for s in self._key_segments] if self.layout == 'legacy' else []
+
+    @property
+    def _compressed_prefix_value_blocks(self) -> list:
+        return [self._legacy_block_state(s) for s in self._value_segments] if self.layout == 'legacy' else []
+
+    @property
+    def _compressed_prefix_key_state(self) -> Optional[dict]:
+        return self._unified_tiled_state(self._key_segments) if self.layout == 'tiled' else None
+
+    @property
+    def _compressed_prefix_value_state(self) -> Optional[dict]:
+        return self._unified_tiled_state(self._value_segments) if self.layout == 'tiled' else None
+
+    @staticmethod
+    def _legacy_block_state(seg) -> dict:
+        """One packed block as ``CompressorBitMap.export_state`` gives it (compress_bitmap_merge.py:693-709):
+        the planes are the segment's; ``block_base`` (inclusive escape count per 128 x gap elements) is
+        counted from the code plane."""
+        nbits, left, right = int(seg.nbits), int(seg.left), int(seg.right)
+        n = int(seg.n_elements)
+        ibs = 128 * _LEGACY_BLOCK_GAPS[nbits - 1]
+        codes = seg.exp_data.reshape(-1)
+        # codes of eight elements form one big-endian nbits-byte word
+        words = codes.view(-1, nbits).to(torch.int64)
+        g = torch.zeros(words.shape[0], dtype=torch.int64, device=codes.device)
+        for i in range(nbits):
+            g = (g << 8) | words[:, i]
+        shifts = torch.arange(7, -1, -1, device=codes.device, dtype=torch.int64) * nbits
+        is_escape = ((g.unsqueeze(1) >> shifts) & ((1 << nbits) - 1)) == 0          # [groups, 8] in element order
+        flat = is_escape.reshape(-1)
+        pad = (-n) % ibs
+        if pad:
+            flat = torch.cat([flat, torch.zeros(pad, dtype=torch.bool, device=flat.device)])
+        block_base = torch.cumsum(flat.view(-1, ibs).sum(dim=1), dim=0)            # int64, as torch.cumsum gives it
+        return {'right': right, 'nbits': nbits, 'left': left, 'left_nbits': left << 7, 'blocksize': 128,
+                'invalid_block_size': ibs, 'device': seg.sign_mass_data.device,
+                'original_shape': torch.Size(seg.original_shape), 'n_elements': n, 'n_exp_data': n * nbits // 8,
+                'sign_mass_data': seg.sign_mass_data.reshape(-1), 'exp_data': codes,
+                'invalid_exp': seg.invalid_exp, 'block_base': block_base}
+
+    @staticmethod
+    def _unified_tiled_state(segments) -> Optional[dict]:
+        """All blocks of one tensor as ONE tiled state, planes in [b][h][tile] order with one running
+        escape count over all tiles (what the reference's 'tiled' layout keeps, :249-329)."""
+        if not segments:
+            return None
+        states = [s.export_state() for s in segments]
+        first = states[0]
+        B, H, T, D = tuple(first['original_shape'])
+        nbits = int(first['nbits'])
+        n = len(states)
+        sm = torch.stack([st['sign_mass_data'].view(B, H, T * D) for st in states], dim=2).reshape(-1)
+        cd = torch.stack([st['exp_data'].view(B, H, T * D * nbits // 8) for st in states], dim=2).reshape(-1)
+        counts, chunks = [], []
+        for st in states:
+            base = st['tile_invalid_base'].to(torch.int64)
+            c = base.clone()
+            c[1:] = base[1:] - base[:-1]
+            counts.append(c.view(B, H))
+            chunks.append(list(torch.split(st['invalid_exp'], [int(v) for v in c.tolist()])))
+        merged_counts = torch.stack(counts, dim=2).reshape(-1)
+        esc = [chunks[j][bh] for bh in range(B * H) for j in range(n)]
+        out = dict(first)
+        out.update(sign_mass_data=sm, exp_data=cd,
+                   invalid_exp=torch.cat(esc) if esc else first['invalid_exp'],
+                   tile_invalid_base=torch.cumsum(merged_counts, dim=0).to(torch.int32),
+                   original_shape=(B, H, T * n, D), num_sequence_tiles=n,
+                   n_elements=sum(int(st['n_elements']) for st in states), kind='tiled_decode')
+        return out
+
     def get_memory(self) -> dict:
         """reference: :1363-1498 (segmented_tiled branch).  Bytes are logical bytes of the packed
         streams plus the dense residual, which counts on both sides."""
@@ -689,6 +806,11 @@ class float11Layer(DynamicLayer):
         k_ratio = v_ratio = 0.0
         for k, v in zip(self._key_segments, self._value_segments):
             km, vm = k.get_memory(), v.get_memory()
+            if self.layout == 'legacy':
+                for seg, mem in ((k, km), (v, vm)):
+                    B, H = int(seg.original_shape[0]), int(seg.original_shape[1])
+                    blocks = -(-seg.n_elements // (128 * _LEGACY_BLOCK_GAPS[int(seg.nbits) - 1]))
+                    mem['compressed_memory'] += 8 * blocks - 4 * B * H      # int64 bases (torch.cumsum promotes)
             compressed += km['compressed_memory'] + vm['compressed_memory']
             original += km['original_memory'] + vm['original_memory']
             k_ratio += k.n_escapes / k.n_elements if k.n_elements else 0.0
@@ -742,6 +864,7 @@ class float11Layer(DynamicLayer):
 
         q_len = key_states.shape[-2]
         prefill_fastpath = q_len > 1 and first_update
+        segmented = self.layout == 'segmented_tiled'
         if key_states.dtype != torch.bfloat16:
             key_states = key_states.to(torch.bfloat16)
         if value_states.dtype != torch.bfloat16:
@@ -756,7 +879,7 @@ class float11Layer(DynamicLayer):
             if n_full > 0:
                 if not self.compress_params_initialized:
                     self._ensure_compress_params_initialized(key_states, value_states)
-                start_segment = len(self._key_segments) if need_adjust else None
+                start_segment = len(self._key_segments) if need_adjust and segmented else None
                 keys_exp_count, values_exp_count = self._pack_span(
                     key_states[:, :, :n_full], value_states[:, :, :n_full], need_adjust)
                 flushed_any = True
@@ -768,12 +891,12 @@ class float11Layer(DynamicLayer):
             self._append_residual(key_states, value_states)
             keys_exp_count, values_exp_count, flushed_any = self._flush_ready_blocks(
                 need_adjust=need_adjust,
-                delay_segmented_block=not prefill_fastpath,
-                collect_adjust_hist=need_adjust and not prefill_fastpath,
+                delay_segmented_block=segmented and not prefill_fastpath,
+                collect_adjust_hist=segmented and need_adjust and not prefill_fastpath,
             )
-        if need_adjust and keys_exp_count is None:
+        if segmented and need_adjust and keys_exp_count is None:
             keys_exp_count, values_exp_count = self._collect_adjust_hist_from_active_residual()
-        if need_adjust:
+        if segmented and need_adjust:
             if prefill_fastpath and flushed_any:
                 self.mark_adjust_recompress_start(0)
             self._update_adjust_params_from_hist(keys_exp_count, values_exp_count)
@@ -919,6 +1042,11 @@ class Float11Cache(Cache):
             # hf_attention.fused_decode: the step's attention reads the packed planes itself
             cache_kwargs = dict(cache_kwargs or {}, float11_skip_materialize=True)
         result = layer.update(key_states, value_states, need_adjust, cache_kwargs)
+        if need_adjust and not self._segmented_adjust and result['keys_exp_count'] is not None:
+            # 'legacy' / 'tiled' layouts: the proposal waits for the next adjust step (reference: :1683-1693)
+            both = codec.read_back(torch.stack([result['keys_exp_count'].to(torch.int32),
+                                                result['values_exp_count'].to(torch.int32)]))
+            layer.adjust_compressor(both[0], both[1])
         if layer_idx == len(self.layers) - 1:
             self.steps += 1
         if fused:

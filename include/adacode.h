@@ -233,6 +233,25 @@ typedef struct adacode_unpack_job {
 int adacode_unpack_jobs(const adacode_unpack_job *jobs, int n_jobs, int B, int H, int seq_tile, int D,
                         int32_t *status, void *stream);
 
+/* Elements per escape-base block of the flat layout for a code length: 128 * {8, 4, 8, 2}[nbits - 1]
+ * (compress_bitmap_merge.py:653-657, invalid_block_size); 0 for an invalid nbits. */
+int adacode_flat_block_elems(int nbits);
+
+/*
+ * Unpack a FLAT packed tensor: n_elems elements (a multiple of adacode_flat_block_elems(nbits)) with
+ * one compact escape list and block_base[i] = number of escapes in blocks 0..i (inclusive).  The planes
+ * are those adacode_pack_tiles writes for tiles of one block each, so a flat tensor is packed by calling
+ * it with B = 1, H = n_elems / block, n_blocks = 1, seq_tile * D = block (tile_base is block_base).
+ * Replaces: CompressorBitMap.uncompress / uncompress_with_weights and the
+ *   uncompress{1,2,3,4}bit_vector_merge kernels (compress_bitmap_merge.py:423-597, :829-873), used by
+ *   the 'legacy' cache layout (float_cache_utils.py:1219-1243) and by the weight hooks (manager.py:46-72).
+ * Most of the tensor is decoded as 16384-element tiles that take their escape offset from every
+ * (16384 / block)-th base.  Needs the pipelined kernels (not available with ADACODE_DISABLE_PIPELINE=1).
+ */
+int adacode_unpack_flat(const uint8_t *sign_mant, const uint8_t *codes, const uint8_t *escapes, int64_t escapes_len,
+                        const int32_t *block_base, int64_t n_elems, int left, int nbits, void *dst_bf16,
+                        int32_t *status, void *stream);
+
 /*
  * hist256 += 256-bin histogram of the exponent field of src[B][H][S][D].
  * Replaces: float11Layer._extract_exponent_histogram (float_cache_utils.py:883-891)

@@ -17,6 +17,9 @@ What is recorded
     seeded histograms, and ``export_initial_compress_parameters`` on a calibration JSON.
   * ``state_machine.json`` — for every scenario in ``tests/scenarios.py`` the digest of the
     reference cache after replaying it.
+  * ``flat_codec_vectors.json`` — digests of what the reference's ``CompressorBitMap.compress``
+    (Triton kernels under the interpreter) produces for flat tensors, ragged sizes included:
+    the flat layout of the 'legacy' cache and of packed model weights.
 
 How the reference is driven for the state-machine scenarios: its ``float_cache_utils`` module
 calls ``compress_tiled_tensor`` and ``materialize_tiled_state`` through module-level names.
@@ -116,6 +119,26 @@ def main() -> None:
     with open(os.path.join(HERE, 'codec_vectors.json'), 'w') as f:
         json.dump({'cases': codec_cases, 'known_answers': known}, f, separators=(',', ':'))
 
+    # ---------------------------------------------------------------- flat codec vectors
+    from kv_compression import compress_bitmap_merge as ref_flat
+    flat_cases = []
+    for nbits in (1, 2, 3, 4):
+        for seed, n_elems, right in ((5, 8192, 129), (6, 3000, 128), (7, 40 * 1024 + 512, 130)):
+            x = synth.kv_tensor((1, 1, n_elems // 8, 8), seed=seed, key_offset=bool(seed & 1)).reshape(-1)
+            c = ref_flat.CompressorBitMap(right=right, nbits=nbits)
+            hist = c.compress(x, need_adjust=True)
+            back = c.uncompress()
+            assert torch.equal(back.view(torch.int16), x.view(torch.int16))
+            flat_cases.append({
+                'seed': seed, 'n_elements': n_elems, 'right': right, 'nbits': nbits,
+                'n_escapes': int(c.invalid_exp.numel()), 'sign_mass_data': scenarios._sha(c.sign_mass_data),
+                'exp_data': scenarios._sha(c.exp_data), 'invalid_exp': scenarios._sha(c.invalid_exp),
+                'block_base': scenarios._sha(c.block_base.to(torch.int64)), 'block_base_dtype': str(c.block_base.dtype),
+                'hist': [int(v) for v in hist.tolist()], 'compressed_memory': int(c.get_memory()['compressed_memory']),
+                'invalid_block_size': int(c.invalid_block_size)})
+    with open(os.path.join(HERE, 'flat_codec_vectors.json'), 'w') as f:
+        json.dump({'cases': flat_cases}, f, separators=(',', ':'))
+
     # ---------------------------------------------------------------- adjuster vectors
     rng = np.random.default_rng(0)
     adj = []
@@ -210,7 +233,12 @@ def main() -> None:
         import warnings
         with warnings.catch_warnings():
             warnings.simplefilter('ignore')
-            digest, _ = scenarios.run_scenario(sc, make_cache, trace_every=16)
+            # The reference's 'tiled' layout hands back only the dense residual from update() (its
+            # materialize_dense has no branch for the unified prefix, float_cache_utils.py:1266-1291: the
+            # consumer was a fused attention module that is no longer in its tree), so the dense
+            # comparison is skipped for it and only the packed state is recorded.
+            dense_ok = sc.cache_kwargs.get('layout') != 'tiled'
+            digest, _ = scenarios.run_scenario(sc, make_cache, trace_every=16, check_dense=dense_ok)
         out[name] = digest
         n_seg = [len(l['key_segments']) for l in digest['layers']]
         print(name, 'segments', n_seg, 'params', [l['params'] for l in digest['layers']],

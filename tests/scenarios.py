@@ -109,6 +109,17 @@ SCENARIOS = {s.name: s for s in [
              dict(right=[(128, 127), (129, 127)], exp_bits=[(3, 4), (3, 4)], compress_rope=True, **_adj()),
              _kv_stream((2, 1, 64), (2, 1, 16), seed=23, prefill=200, decode=200, layers=2),
              config_extra=dict(kv_lora_rank=64, qk_rope_head_dim=16)),
+    # flat ('legacy') layout: every full block is packed at once, also in decode; windows proposed on
+    # an adjust step are adopted at the next one (period 64 is NOT rounded for this layout)
+    Scenario('legacy_layout_adjust', 'float11', 1,
+             dict(right=[(128, 128)], exp_bits=[(3, 3)], need_adjust=True, update_steps=64, residual_length=0,
+                  block_size=128, layout='legacy'),
+             _kv_stream((1, 2, 32), (1, 2, 32), seed=31, prefill=200, decode=330, scale_after=260, scale=64.0)),
+    # unified 'tiled' layout without the adjuster: one state per tensor, planes in [b][h][tile] order
+    Scenario('tiled_layout_fixed', 'float11', 1,
+             dict(right=[(129, 128)], exp_bits=[(3, 4)], need_adjust=False, update_steps=0, residual_length=0,
+                  block_size=128, layout='tiled'),
+             _kv_stream((2, 2, 32), (2, 2, 32), seed=37, prefill=300, decode=260)),
     # MLA with the rope key kept dense
     Scenario('mla_dense_rope', 'mla', 1,
              dict(right=[(128, 127)], exp_bits=[(3, 4)], compress_rope=False, **_adj()),
@@ -146,11 +157,42 @@ _MEMORY_KEYS = (
 )
 
 
+def _n_packed_blocks(layer) -> int:
+    layout = getattr(layer, 'layout', 'segmented_tiled')
+    if layout == 'legacy':
+        return len(layer._compressed_prefix_key_blocks)
+    if layout == 'tiled':
+        st = layer._compressed_prefix_key_state
+        return 0 if st is None else int(st['num_sequence_tiles'])
+    return len(layer._compressed_prefix_key_segments)
+
+
+def legacy_block_digest(state: dict) -> dict:
+    """Digest of one flat ('legacy') block state (``CompressorBitMap.export_state``)."""
+    return {
+        'right': int(state['right']), 'nbits': int(state['nbits']), 'left': int(state['left']),
+        'shape': [int(v) for v in state['original_shape']], 'n_escapes': int(state['invalid_exp'].numel()),
+        'sign_mass_data': _sha(state['sign_mass_data']), 'exp_data': _sha(state['exp_data']),
+        'invalid_exp': _sha(state['invalid_exp']), 'block_base': _sha(state['block_base'].to(torch.int64)),
+    }
+
+
 def layer_digest(layer) -> dict:
     mem = layer.get_memory()
+    layout = getattr(layer, 'layout', 'segmented_tiled')
+    if layout == 'legacy':
+        key_part = [legacy_block_digest(s) for s in layer._compressed_prefix_key_blocks]
+        value_part = [legacy_block_digest(s) for s in layer._compressed_prefix_value_blocks]
+    elif layout == 'tiled':
+        ks, vs = layer._compressed_prefix_key_state, layer._compressed_prefix_value_state
+        key_part = [] if ks is None else [segment_digest(ks)]
+        value_part = [] if vs is None else [segment_digest(vs)]
+    else:
+        key_part = [segment_digest(s) for s in layer._compressed_prefix_key_segments]
+        value_part = [segment_digest(s) for s in layer._compressed_prefix_value_segments]
     out = {
-        'key_segments': [segment_digest(s) for s in layer._compressed_prefix_key_segments],
-        'value_segments': [segment_digest(s) for s in layer._compressed_prefix_value_segments],
+        'key_segments': key_part,
+        'value_segments': value_part,
         'memory': {k: mem[k] for k in _MEMORY_KEYS},
         'params': [int(layer.keys_right), int(layer.keys_nbits), int(layer.values_right), int(layer.values_nbits)],
         'new_params': [int(layer.new_keys_right), int(layer.new_keys_nbits), int(layer.new_values_right),
@@ -187,10 +229,10 @@ def run_scenario(sc: Scenario, make_cache, device='cpu', check_dense: bool = Tru
         if trace_every and (step % trace_every == 0):
             snapshots.append({'step': step, 'layers': [
                 {'params': [int(x.keys_right), int(x.keys_nbits), int(x.values_right), int(x.values_nbits)],
-                 'n_segments': len(x._compressed_prefix_key_segments)} for x in cache.layers]})
+                 'n_segments': _n_packed_blocks(x)} for x in cache.layers]})
     digest = {'layers': [layer_digest(x) for x in cache.layers], 'snapshots': snapshots,
               'steps': int(cache.steps), 'update_steps': int(cache.update_steps)}
-    for l in range(sc.num_layers):
+    for l in range(sc.num_layers if check_dense else 0):
         mk, mv = cache.materialize_layer(l)
         assert torch.equal(mk.cpu().view(torch.int16), torch.cat(seen_k[l], dim=-2).view(torch.int16))
         assert torch.equal(mv.cpu().view(torch.int16), torch.cat(seen_v[l], dim=-2).view(torch.int16))
