@@ -10,6 +10,7 @@
 //            a warp scan plus an 8-entry cross-warp prefix
 // Both kernels are bandwidth work: no tensor cores, no reshaping into GEMMs.
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -702,30 +703,52 @@ int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
     return launch_unpack_pipe(ja, st);
 }
 
-template <int N>
-int launch_pack_pipe_n(const PackPipeArgs &pa, bool hist, cudaStream_t st) {
-    const int grid = grid_for(pa.n_tiles, 2);
-    if (hist) {
-        int rc = ensure_dynamic_smem(k_pack_pipe<N, true>, sizeof(PackSmem));
-        if (rc != ADACODE_OK) return rc;
-        k_pack_pipe<N, true><<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
-    } else {
-        int rc = ensure_dynamic_smem(k_pack_pipe<N, false>, sizeof(PackSmem));
-        if (rc != ADACODE_OK) return rc;
-        k_pack_pipe<N, false><<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+// Small launches end with the fused tail (a cooperative launch: all CTAs are resident and meet at one
+// grid-wide barrier) instead of the last-CTA scan plus a compaction kernel.
+bool fused_tail_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = getenv("ADACODE_DISABLE_FUSED_TAIL");
+        int dev = 0, coop = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess)
+            coop = 0;
+        cached = (coop && !(e && e[0] == '1')) ? 1 : 0;
     }
-    ADACODE_CUDA_TRY(cudaGetLastError());
+    return cached == 1;
+}
+
+template <typename Kernel>
+int launch_pack_kernel(Kernel kernel, const PackPipeArgs &pa, int grid, cudaStream_t st) {
+    int rc = ensure_dynamic_smem(kernel, sizeof(PackSmem));
+    if (rc != ADACODE_OK) return rc;
+    if (pa.fused_tail) {
+        void *args[] = {(void *)&pa};
+        ADACODE_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)kernel, dim3(grid), dim3(kPipeThreads), args,
+                                                     sizeof(PackSmem), st));
+    } else {
+        kernel<<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+        ADACODE_CUDA_TRY(cudaGetLastError());
+    }
     return ADACODE_OK;
 }
 
-// Pipelined pack of all jobs of `pa` with one pack launch and one compaction launch.
-int launch_pack_pipe(const PackPipeArgs &pa, int nbits, cudaStream_t st) {
+template <int N>
+int launch_pack_pipe_n(const PackPipeArgs &pa, bool hist, cudaStream_t st) {
+    const int grid = grid_for(pa.n_tiles, 2);
+    return hist ? launch_pack_kernel(k_pack_pipe<N, true>, pa, grid, st)
+                : launch_pack_kernel(k_pack_pipe<N, false>, pa, grid, st);
+}
+
+// Pipelined pack of all jobs of `pa` with one pack launch and, for large launches, one compaction launch.
+int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
     bool hist = false;
     int max_blocks = 0;
     for (int j = 0; j < pa.n_jobs; ++j) {
         hist = hist || pa.job[j].hist != nullptr;
         max_blocks = pa.job[j].n_blocks > max_blocks ? pa.job[j].n_blocks : max_blocks;
     }
+    pa.fused_tail = (pa.n_tiles <= kFusedTailMaxTiles && fused_tail_enabled()) ? 1 : 0;
     int rc;
     switch (nbits) {
         case 1: rc = launch_pack_pipe_n<1>(pa, hist, st); break;
@@ -733,7 +756,7 @@ int launch_pack_pipe(const PackPipeArgs &pa, int nbits, cudaStream_t st) {
         case 3: rc = launch_pack_pipe_n<3>(pa, hist, st); break;
         default: rc = launch_pack_pipe_n<4>(pa, hist, st); break;
     }
-    if (rc != ADACODE_OK) return rc;
+    if (rc != ADACODE_OK || pa.fused_tail) return rc;
     // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
     const int64_t job_tiles = (int64_t)max_blocks * pa.BH;
     const int64_t want = (job_tiles + kWarps - 1) / kWarps;

@@ -25,6 +25,10 @@ constexpr int kPipeThreads = kConsumerThreads + 32;
 constexpr int kUnitElems = 16384;
 constexpr int kStages = 2;
 constexpr uint32_t kMaxPolls = 1u << 22;
+#ifndef ADACODE_SWIZZLE_HALVES
+#define ADACODE_SWIZZLE_HALVES 1
+#endif
+constexpr bool kSwizzleHalves = ADACODE_SWIZZLE_HALVES != 0;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -397,13 +401,18 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
     static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
     const int c0 = warp * (kPCPT * 32) + lane;
+    // A lane's chunk is 32 bytes: two 16-byte stores at a 32-byte lane stride would hit every bank
+    // twice.  Lanes 4-7 of every eight store their halves in the opposite order, so that each store
+    // instruction covers all banks once.
+    const bool flip = kSwizzleHalves && (lane & 4);
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = c0 + k * 32;
         if (c < chunks) {
-            uint16_t *ow = s.out + c * 16;
-            reinterpret_cast<uint4 *>(ow)[0] = o[k][0];
-            reinterpret_cast<uint4 *>(ow)[1] = o[k][1];
+            uint4 *ow = reinterpret_cast<uint4 *>(s.out + c * 16);
+            const uint4 first = flip ? o[k][1] : o[k][0], second = flip ? o[k][0] : o[k][1];
+            ow[flip ? 1 : 0] = first;
+            ow[flip ? 0 : 1] = second;
         }
     }
     if (zc[0] + zc[1] != 0) {
@@ -685,7 +694,10 @@ struct PackPipeArgs {
     int unit_rows, units_per_tile;
     int32_t *status;
     uint32_t poll_limit;      // bound of every on-chip wait (kMaxPolls unless a test lowered it)
+    int fused_tail;           // cooperative launch: every CTA places its own tiles' escapes after a grid barrier
 };
+
+constexpr int kFusedTailMaxTiles = 8192;     // the whole prefix array lives in shared memory
 
 __device__ __forceinline__ int job_of_tile(const PackPipeArgs &pa, int64_t tile) {
     int j = 0;
@@ -758,6 +770,97 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
     if (tid == 0) *pa.done = 0u;
 }
 
+__device__ __forceinline__ void compact_tile_units(const PackPipeArgs &pa, const PackJob &jb, int64_t t, int64_t dst,
+                                                   int c, int *my_hist, bool do_hist);
+
+// Tail of a cooperative pack launch (small launches): after a grid-wide barrier every CTA scans ALL
+// tile counts itself (a few KB from L2, the inclusive prefixes stay in shared memory, aliased onto
+// the idle output stagings) and then writes the tile bases and segment offsets of ITS tiles and
+// moves their escape bytes into place, one warp per tile.  This replaces the last-CTA scan, the
+// launch gap and the compaction kernel, which together cost more than a small pack itself.
+template <bool HIST>
+__device__ __forceinline__ void fused_tail(const PackPipeArgs &pa, PackSmem &s) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int *prefix = reinterpret_cast<int *>(s.sm);            // sm, codes and esc stagings are contiguous: 40 KB
+    static_assert(offsetof(PackSmem, esc) + sizeof(s.esc) - offsetof(PackSmem, sm) >= kFusedTailMaxTiles * sizeof(int),
+                  "the prefix array must fit the output stagings");
+    int *warp_hist = reinterpret_cast<int *>(s.stage[0].in);        // [kPWarps][2][256] ints = 32 KB
+    const int n_tiles = (int)pa.n_tiles;
+    // inclusive scan of all tile counts into shared memory
+    if (tid == 0) s.carry = 0;
+    consumer_sync();
+    const int per_pass = kConsumerThreads * kScanRun;
+    for (int pass = 0; pass < n_tiles; pass += per_pass) {
+        const int t0 = pass + tid * kScanRun;
+        int c[kScanRun];
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < n_tiles) ? __ldcg(pa.tile_counts + t0 + i) : 0;
+        int run = 0;
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) run += c[i];
+        int x = run;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(kFull, x, d);
+            if (lane >= d) x += u;
+        }
+        if (lane == 31) s.scan[warp] = x;
+        consumer_sync();
+        int wp = 0, tot = 0;
+#pragma unroll
+        for (int i = 0; i < kPWarps; ++i) {
+            const int v = s.scan[i];
+            wp += (i < warp) ? v : 0;
+            tot += v;
+        }
+        int incl = (int)s.carry + wp + (x - run);
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) {
+            incl += c[i];
+            if (t0 + i < n_tiles) prefix[t0 + i] = incl;
+        }
+        consumer_sync();
+        if (tid == 0) s.carry += tot;
+    }
+    consumer_sync();
+    // this CTA's tiles, job by job (the escaped exponents of a job are counted into that job's histogram)
+    for (int j = 0; j < pa.n_jobs; ++j) {
+        const PackJob &jb = pa.job[j];
+        const bool do_hist = HIST && jb.hist != nullptr;
+        if (do_hist) {
+            for (int i = tid; i < kPWarps * 2 * 256; i += kConsumerThreads) warp_hist[i] = 0;
+            consumer_sync();
+        }
+        int *my_hist = warp_hist + (warp * 2 + (lane & 1)) * 256;
+        const int64_t job_end = jb.tile0 + (int64_t)jb.n_blocks * pa.BH;
+        const int job_base = jb.tile0 > 0 ? prefix[jb.tile0 - 1] : 0;
+        if (blockIdx.x == 0 && tid == 0) jb.seg_off[0] = 0;
+        // first tile of this CTA inside the job, then every gridDim.x-th; warp w takes every kPWarps-th of them
+        int64_t first = jb.tile0 + ((int64_t)blockIdx.x - jb.tile0 % gridDim.x + gridDim.x) % gridDim.x;
+        for (int64_t t = first + (int64_t)warp * gridDim.x; t < job_end; t += (int64_t)kPWarps * gridDim.x) {
+            const int incl = prefix[t];
+            const int c = incl - (t > 0 ? prefix[t - 1] : 0);
+            const int64_t gb = t / pa.BH;
+            const int blk_base = gb * pa.BH > 0 ? prefix[gb * pa.BH - 1] : 0;
+            if (lane == 0) {
+                jb.tile_base[t - jb.tile0] = incl - blk_base;
+                if ((t + 1) % pa.BH == 0) jb.seg_off[gb + 1 - jb.blk0] = (int64_t)(incl - job_base);
+            }
+            if (c != 0) compact_tile_units(pa, jb, t, (int64_t)(incl - c - job_base), c, my_hist, do_hist);
+        }
+        if (do_hist) {
+            consumer_sync();
+            if (tid < 256) {
+                int total = 0;
+#pragma unroll 4
+                for (int i = 0; i < kPWarps * 2; ++i) total += warp_hist[i * 256 + tid];
+                if (total != 0) atomicAdd(jb.hist + tid, total);
+            }
+            consumer_sync();
+        }
+    }
+}
+
 // Per-thread in-window counters (16-bit fields) -> the CTA's shared histogram.
 template <int N>
 __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::v], int left, int *s_hist) {
@@ -791,9 +894,13 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
         const bool valid = c < chunks;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
         if (valid) {
+            // 32 bytes per lane: lanes 4-7 of every eight load their halves in the opposite order, so
+            // that each 16-byte load instruction covers all banks once (see unpack_unit)
             const uint4 *p = reinterpret_cast<const uint4 *>(st.in + c * 16);
-            w0 = p[0];
-            w1 = p[1];
+            const bool flip = kSwizzleHalves && (lane & 4);
+            const uint4 a = p[flip ? 1 : 0], b = p[flip ? 0 : 1];
+            w0 = flip ? b : a;
+            w1 = flip ? a : b;
         }
         const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         uint32_t smw[4];
@@ -991,6 +1098,34 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
     bulk_wait_all();
     __threadfence();
     consumer_sync();
+    if (pa.fused_tail) {
+        // Grid-wide barrier of a cooperative launch (all CTAs are resident): arrive, then wait with a
+        // bound for the others.  A second counter tells the last CTA to leave when both can be cleared.
+        if (tid == 0) {
+            atomicAdd(pa.done, 1u);
+            uint32_t polls = 0;
+            while (*reinterpret_cast<volatile unsigned int *>(pa.done) < gridDim.x) {
+                __nanosleep(64);
+                if (++polls > pa.poll_limit) {
+                    atomicOr(pa.status, ADACODE_STATUS_TIMEOUT);
+                    break;
+                }
+            }
+            __threadfence();
+        }
+        consumer_sync();
+        fused_tail<HIST>(pa, s);
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) {
+            const unsigned left_before = atomicAdd(pa.done + 1, 1u);
+            if (left_before == gridDim.x - 1) {
+                pa.done[0] = 0u;
+                pa.done[1] = 0u;
+            }
+        }
+        return;
+    }
     if (tid == 0) {
         const unsigned ticket = atomicAdd(pa.done, 1u);
         s.is_last = (ticket == gridDim.x - 1);
@@ -1001,12 +1136,69 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
     scan_tile_counts(pa, &s.carry, s.scan);
 }
 
+// One warp copies the escape bytes of tile t (its units follow each other in the scratch) to `dst`
+// of its job's stream.  The bytes move as aligned 32-bit words: the source words are funnel-shifted
+// into the alignment of the destination; only the first and last word of a run use byte stores.
+// With do_hist the escaped exponents are counted into `my_hist` (256 bins in shared memory).
+__device__ __forceinline__ void compact_tile_units(const PackPipeArgs &pa, const PackJob &jb, int64_t t, int64_t dst,
+                                                   int c, int *my_hist, bool do_hist) {
+    const int lane = threadIdx.x & 31;
+    const int upt = pa.units_per_tile;
+    const int unit_elems = pa.unit_rows * pa.D;
+    const bool fits = dst >= 0 && dst + c <= jb.capacity;
+    if (!fits && lane == 0) atomicOr(pa.status, ADACODE_STATUS_ESCAPE_OVERFLOW);
+    for (int u = 0; u < upt; ++u) {
+        const int cu = __ldcg(pa.unit_counts + t * upt + u);
+        // unit slots start on 16-byte boundaries
+        const uint32_t *src4 =
+            reinterpret_cast<const uint32_t *>(pa.esc_scratch + t * pa.tile_elems + (int64_t)u * unit_elems);
+        uint8_t *d8 = jb.escapes + dst;
+        const int r = (int)((uintptr_t)d8 & 3);
+        uint32_t *dst32 = reinterpret_cast<uint32_t *>(d8 - r);
+        const int n_words = (r + cu + 3) >> 2;             // destination words touched
+        // four destination words (16 bytes) per lane and step: one 16-byte load of the source
+        // words behind them plus the word before (for the shift)
+        const uint4 *src16 = reinterpret_cast<const uint4 *>(src4);
+        const int n_quads = (n_words + 3) >> 2;
+#pragma unroll 2
+        for (int q = lane; q < n_quads; q += 32) {
+            const uint4 cur = 16 * q < cu ? __ldcg(src16 + q) : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t prev = (r != 0 && q > 0) ? __ldcg(src4 + 4 * q - 1) : 0u;
+            const uint32_t w[5] = {prev, cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int j = 4 * q + k;                       // destination word
+                const int s0 = 4 * j - r;                      // source index of the byte that lands in its byte 0
+                const uint32_t v = r != 0 ? __funnelshift_r(w[k], w[k + 1], 8 * (4 - r)) : w[k + 1];
+                if (fits && j < n_words) {
+                    if (s0 >= 0 && s0 + 4 <= cu) {
+                        dst32[j] = v;
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < 4; ++b)
+                            if (s0 + b >= 0 && s0 + b < cu)
+                                reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
+                    }
+                }
+                if (do_hist) {
+                    // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
+                    uint32_t x = w[k + 1];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        if (4 * j + b < cu) atomicAdd(my_hist + (x & 0xFFu), 1);
+                        x >>= 8;
+                    }
+                }
+            }
+        }
+        dst += cu;
+    }
+}
+
 // Gather every unit's escape bytes from its scratch slot into the compact per-segment stream.
 // Tile t of global block i starts at blk_off[i] - blk_off[first block of the job] + tile_base[t] -
-// count[t] in its job's stream; its units follow each other.  blockIdx.y is the job.
-// One warp per tile.  All of a tile's metadata is fetched with independent loads (one memory round
-// trip), the bytes move as aligned 32-bit words (the source words are funnel-shifted into the
-// alignment of the destination; only the first and last word of a run use byte stores).
+// count[t] in its job's stream.  blockIdx.y is the job; one warp per tile; all of a tile's metadata
+// is fetched with independent loads (one memory round trip).
 // With HIST the escaped exponents are counted here (whole warps of escape bytes) rather than one
 // by one inside the pack kernel.  Escaped exponents cluster on a few values, so each warp keeps
 // four copies of the 256 bins (picked by lane & 3): one copy would serialise most of a warp's
@@ -1026,8 +1218,6 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const __grid_constan
     const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t n_warps = (int64_t)gridDim.x * kWarps;
     const int64_t job_tiles = (int64_t)jb.n_blocks * pa.BH;
-    const int upt = pa.units_per_tile;
-    const int unit_elems = pa.unit_rows * pa.D;
     const int64_t job_off = __ldg(pa.blk_off + jb.blk0);
     for (int64_t lt = warp_global; lt < job_tiles; lt += n_warps) {
         const int64_t t = jb.tile0 + lt;
@@ -1035,57 +1225,8 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const __grid_constan
         const int c = __ldg(pa.tile_counts + t);
         const int tb = __ldg(jb.tile_base + lt);
         const int64_t so = __ldg(pa.blk_off + t / pa.BH) - job_off;
-        int cu = __ldg(pa.unit_counts + t * upt);
         if (c == 0) continue;
-        int64_t dst = so + tb - c;
-        const bool fits = dst >= 0 && dst + c <= jb.capacity;
-        if (!fits && lane == 0) atomicOr(pa.status, ADACODE_STATUS_ESCAPE_OVERFLOW);
-        for (int u = 0; u < upt; ++u) {
-            if (u > 0) cu = __ldg(pa.unit_counts + t * upt + u);
-            // unit slots start on 16-byte boundaries
-            const uint32_t *src4 =
-                reinterpret_cast<const uint32_t *>(pa.esc_scratch + t * pa.tile_elems + (int64_t)u * unit_elems);
-            uint8_t *d8 = jb.escapes + dst;
-            const int r = (int)((uintptr_t)d8 & 3);
-            uint32_t *dst32 = reinterpret_cast<uint32_t *>(d8 - r);
-            const int n_words = (r + cu + 3) >> 2;             // destination words touched
-            // four destination words (16 bytes) per lane and step: one 16-byte load of the source
-            // words behind them plus the word before (for the shift)
-            const uint4 *src16 = reinterpret_cast<const uint4 *>(src4);
-            const int n_quads = (n_words + 3) >> 2;
-#pragma unroll 2
-            for (int q = lane; q < n_quads; q += 32) {
-                const uint4 cur = 16 * q < cu ? src16[q] : make_uint4(0u, 0u, 0u, 0u);
-                const uint32_t prev = (r != 0 && q > 0) ? src4[4 * q - 1] : 0u;
-                const uint32_t w[5] = {prev, cur.x, cur.y, cur.z, cur.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int j = 4 * q + k;                       // destination word
-                    const int s0 = 4 * j - r;                      // source index of the byte that lands in its byte 0
-                    const uint32_t v = r != 0 ? __funnelshift_r(w[k], w[k + 1], 8 * (4 - r)) : w[k + 1];
-                    if (fits && j < n_words) {
-                        if (s0 >= 0 && s0 + 4 <= cu) {
-                            dst32[j] = v;
-                        } else {
-#pragma unroll
-                            for (int b = 0; b < 4; ++b)
-                                if (s0 + b >= 0 && s0 + b < cu)
-                                    reinterpret_cast<uint8_t *>(dst32 + j)[b] = (uint8_t)(v >> (8 * b));
-                        }
-                    }
-                    if (do_hist) {
-                        // source word j holds source bytes 4j .. 4j+3: each source byte is counted once
-                        uint32_t x = w[k + 1];
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            if (4 * j + b < cu) atomicAdd(my_hist + (x & 0xFFu), 1);
-                            x >>= 8;
-                        }
-                    }
-                }
-            }
-            dst += cu;
-        }
+        compact_tile_units(pa, jb, t, so + tb - c, c, my_hist, do_hist);
     }
     if (do_hist) {
         __syncthreads();

@@ -74,7 +74,8 @@ def workload_config(world: int) -> dict:
         'sequences_per_gpu': S4_BATCH // world, 'block_size': BLOCK,
         'l2': 'per-rank working set of a step (inputs + planes) exceeds L2 many times over; all layers are packed '
               'before any is unpacked, so nothing is re-read from L2',
-        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs)',
+        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs); launches of '
+                    'neighbouring layers alternate between two streams',
     }
 
 
@@ -387,13 +388,21 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     esc_base = esc_base.to(dev)
     n_elems = sum(x.numel() for ent in slots for x in ent['x'])
     tiles_per_launch = 2 * per * S4_HEADS * (half // BLOCK)
-    ws = torch.zeros(L.adacode_pack_workspace_bytes(tiles_per_launch, BLOCK * S4_DIM), dtype=torch.uint8, device=dev)
+    # launches of neighbouring layers alternate between two streams (each with its own pack scratch and
+    # unpack destination): the tail of one launch and the compaction pass overlap the next launch
+    worker = torch.cuda.Stream(dev)
+    lanes = (main, worker)
+    ws2 = [torch.zeros(L.adacode_pack_workspace_bytes(tiles_per_launch, BLOCK * S4_DIM), dtype=torch.uint8, device=dev)
+           for _ in lanes]
+    fork, join = torch.cuda.Event(), torch.cuda.Event()
     hists = torch.zeros((n_layers, 2, 2, 256), dtype=torch.int32, device=dev)       # [layer][span][k/v]
     hists_red = torch.zeros((n_layers, 2, 256), dtype=torch.int32, device=dev)      # span B, summed over ranks
     params_dev = torch.zeros((n_layers * 2, 2), dtype=torch.int32, device=dev)
     params_host = torch.zeros((n_layers * 2, 2), dtype=torch.int32).pin_memory()
     status = torch.zeros(2, dtype=torch.int32, device=dev)
-    out = [torch.empty((per, S4_HEADS, S4_SEQ, S4_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    out2 = [[torch.empty((per, S4_HEADS, S4_SEQ, S4_DIM), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+            for _ in lanes]
+    out = out2[0]
     side = torch.cuda.Stream(dev)
     ev_packed, ev_params = torch.cuda.Event(), torch.cuda.Event()
     rec_dtype = codec._segment_dtype()
@@ -402,8 +411,18 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     tables_dirty = [True] * n_layers
     launches = {'pack': 0, 'unpack': 0}
 
-    def pack_layer(li: int) -> None:
+    def on_lanes(fn, n_lanes: int) -> None:
+        if n_lanes > 1:
+            fork.record(main)
+            worker.wait_event(fork)
+        fn(n_lanes)
+        if n_lanes > 1:
+            join.record(worker)
+            main.wait_event(join)
+
+    def pack_layer(li: int, si: int = 0) -> None:
         ent = slots[li]
+        ws, stream = ws2[si], lanes[si].cuda_stream
         for si, span in enumerate(('a', 'b')):
             pair = ent[span]
             groups = [pair] if pair[0].nbits == pair[1].nbits else [[pair[0]], [pair[1]]]
@@ -449,12 +468,13 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         t64[..., 2] = esc_base + offsets_all[..., :-1]
         t64[..., 4] = offsets_all[..., 1:] - offsets_all[..., :-1]
 
-    def unpack_layer(li: int) -> None:
+    def unpack_layer(li: int, si: int = 0) -> None:
         jobs = (_lib.UnpackJob * 2)()
+        stream = lanes[si].cuda_stream
         for wi in range(2):
-            db, dh, ds, _ = out[wi].stride()
+            db, dh, ds, _ = out2[si][wi].stride()
             jobs[wi].segments_dev, jobs[wi].n_segments = tables_dev[li, wi].data_ptr(), nseg
-            jobs[wi].dst_bf16 = out[wi].data_ptr()
+            jobs[wi].dst_bf16 = out2[si][wi].data_ptr()
             jobs[wi].dstride_b, jobs[wi].dstride_h, jobs[wi].dstride_s = db, dh, ds
         rc = L.adacode_unpack_jobs(ctypes.addressof(jobs), 2, per, S4_HEADS, BLOCK, S4_DIM, status.data_ptr(), stream)
         if rc:
@@ -487,8 +507,8 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         hists.zero_()
         if ev:
             ev[0].record(main)
-        for li in range(n_layers):
-            pack_layer(li)
+        n_lanes = 1 if check is not None else 2
+        on_lanes(lambda nl: [pack_layer(li, li % nl) for li in range(n_layers)], n_lanes)
         if ev:
             ev[1].record(main)
         # the adjuster's exchange: span-B histograms summed over all ranks, then the device-side
@@ -508,9 +528,11 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         complete_tables()
         if ev:
             ev[2].record(main)
-        for li in range(n_layers):
-            unpack_layer(li)
-            if check is not None:
+        if check is None:
+            on_lanes(lambda nl: [unpack_layer(li, li % nl) for li in range(n_layers)], n_lanes)
+        else:
+            for li in range(n_layers):
+                unpack_layer(li)
                 check(li)
         if ev:
             ev[3].record(main)
