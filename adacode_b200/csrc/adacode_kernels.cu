@@ -703,33 +703,12 @@ int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
     return launch_unpack_pipe(ja, st);
 }
 
-// Small launches end with the fused tail (a cooperative launch: all CTAs are resident and meet at one
-// grid-wide barrier) instead of the last-CTA scan plus a compaction kernel.
-bool fused_tail_enabled() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char *e = getenv("ADACODE_DISABLE_FUSED_TAIL");
-        int dev = 0, coop = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess)
-            coop = 0;
-        cached = (coop && !(e && e[0] == '1')) ? 1 : 0;
-    }
-    return cached == 1;
-}
-
 template <typename Kernel>
 int launch_pack_kernel(Kernel kernel, const PackPipeArgs &pa, int grid, cudaStream_t st) {
     int rc = ensure_dynamic_smem(kernel, sizeof(PackSmem));
     if (rc != ADACODE_OK) return rc;
-    if (pa.fused_tail) {
-        void *args[] = {(void *)&pa};
-        ADACODE_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)kernel, dim3(grid), dim3(kPipeThreads), args,
-                                                     sizeof(PackSmem), st));
-    } else {
-        kernel<<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
-        ADACODE_CUDA_TRY(cudaGetLastError());
-    }
+    kernel<<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+    ADACODE_CUDA_TRY(cudaGetLastError());
     return ADACODE_OK;
 }
 
@@ -740,7 +719,7 @@ int launch_pack_pipe_n(const PackPipeArgs &pa, bool hist, cudaStream_t st) {
                 : launch_pack_kernel(k_pack_pipe<N, false>, pa, grid, st);
 }
 
-// Pipelined pack of all jobs of `pa` with one pack launch and, for large launches, one compaction launch.
+// Pipelined pack of all jobs of `pa` with one pack launch and one compaction launch.
 int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
     bool hist = false;
     int max_blocks = 0;
@@ -748,7 +727,6 @@ int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
         hist = hist || pa.job[j].hist != nullptr;
         max_blocks = pa.job[j].n_blocks > max_blocks ? pa.job[j].n_blocks : max_blocks;
     }
-    pa.fused_tail = (pa.n_tiles <= kFusedTailMaxTiles && fused_tail_enabled()) ? 1 : 0;
     int rc;
     switch (nbits) {
         case 1: rc = launch_pack_pipe_n<1>(pa, hist, st); break;
@@ -756,7 +734,7 @@ int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
         case 3: rc = launch_pack_pipe_n<3>(pa, hist, st); break;
         default: rc = launch_pack_pipe_n<4>(pa, hist, st); break;
     }
-    if (rc != ADACODE_OK || pa.fused_tail) return rc;
+    if (rc != ADACODE_OK) return rc;
     // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
     const int64_t job_tiles = (int64_t)max_blocks * pa.BH;
     const int64_t want = (job_tiles + kWarps - 1) / kWarps;

@@ -25,10 +25,6 @@ constexpr int kPipeThreads = kConsumerThreads + 32;
 constexpr int kUnitElems = 16384;
 constexpr int kStages = 2;
 constexpr uint32_t kMaxPolls = 1u << 22;
-#ifndef ADACODE_SWIZZLE_HALVES
-#define ADACODE_SWIZZLE_HALVES 1
-#endif
-constexpr bool kSwizzleHalves = ADACODE_SWIZZLE_HALVES != 0;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -401,18 +397,13 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
     static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
     const int c0 = warp * (kPCPT * 32) + lane;
-    // A lane's chunk is 32 bytes: two 16-byte stores at a 32-byte lane stride would hit every bank
-    // twice.  Lanes 4-7 of every eight store their halves in the opposite order, so that each store
-    // instruction covers all banks once.
-    const bool flip = kSwizzleHalves && (lane & 4);
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = c0 + k * 32;
         if (c < chunks) {
-            uint4 *ow = reinterpret_cast<uint4 *>(s.out + c * 16);
-            const uint4 first = flip ? o[k][1] : o[k][0], second = flip ? o[k][0] : o[k][1];
-            ow[flip ? 1 : 0] = first;
-            ow[flip ? 0 : 1] = second;
+            uint16_t *ow = s.out + c * 16;
+            reinterpret_cast<uint4 *>(ow)[0] = o[k][0];
+            reinterpret_cast<uint4 *>(ow)[1] = o[k][1];
         }
     }
     if (zc[0] + zc[1] != 0) {
@@ -694,10 +685,7 @@ struct PackPipeArgs {
     int unit_rows, units_per_tile;
     int32_t *status;
     uint32_t poll_limit;      // bound of every on-chip wait (kMaxPolls unless a test lowered it)
-    int fused_tail;           // cooperative launch: every CTA places its own tiles' escapes after a grid barrier
 };
-
-constexpr int kFusedTailMaxTiles = 8192;     // the whole prefix array lives in shared memory
 
 __device__ __forceinline__ int job_of_tile(const PackPipeArgs &pa, int64_t tile) {
     int j = 0;
@@ -770,97 +758,6 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
     if (tid == 0) *pa.done = 0u;
 }
 
-__device__ __forceinline__ void compact_tile_units(const PackPipeArgs &pa, const PackJob &jb, int64_t t, int64_t dst,
-                                                   int c, int *my_hist, bool do_hist);
-
-// Tail of a cooperative pack launch (small launches): after a grid-wide barrier every CTA scans ALL
-// tile counts itself (a few KB from L2, the inclusive prefixes stay in shared memory, aliased onto
-// the idle output stagings) and then writes the tile bases and segment offsets of ITS tiles and
-// moves their escape bytes into place, one warp per tile.  This replaces the last-CTA scan, the
-// launch gap and the compaction kernel, which together cost more than a small pack itself.
-template <bool HIST>
-__device__ __forceinline__ void fused_tail(const PackPipeArgs &pa, PackSmem &s) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int *prefix = reinterpret_cast<int *>(s.sm);            // sm, codes and esc stagings are contiguous: 40 KB
-    static_assert(offsetof(PackSmem, esc) + sizeof(s.esc) - offsetof(PackSmem, sm) >= kFusedTailMaxTiles * sizeof(int),
-                  "the prefix array must fit the output stagings");
-    int *warp_hist = reinterpret_cast<int *>(s.stage[0].in);        // [kPWarps][2][256] ints = 32 KB
-    const int n_tiles = (int)pa.n_tiles;
-    // inclusive scan of all tile counts into shared memory
-    if (tid == 0) s.carry = 0;
-    consumer_sync();
-    const int per_pass = kConsumerThreads * kScanRun;
-    for (int pass = 0; pass < n_tiles; pass += per_pass) {
-        const int t0 = pass + tid * kScanRun;
-        int c[kScanRun];
-#pragma unroll
-        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < n_tiles) ? __ldcg(pa.tile_counts + t0 + i) : 0;
-        int run = 0;
-#pragma unroll
-        for (int i = 0; i < kScanRun; ++i) run += c[i];
-        int x = run;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int u = __shfl_up_sync(kFull, x, d);
-            if (lane >= d) x += u;
-        }
-        if (lane == 31) s.scan[warp] = x;
-        consumer_sync();
-        int wp = 0, tot = 0;
-#pragma unroll
-        for (int i = 0; i < kPWarps; ++i) {
-            const int v = s.scan[i];
-            wp += (i < warp) ? v : 0;
-            tot += v;
-        }
-        int incl = (int)s.carry + wp + (x - run);
-#pragma unroll
-        for (int i = 0; i < kScanRun; ++i) {
-            incl += c[i];
-            if (t0 + i < n_tiles) prefix[t0 + i] = incl;
-        }
-        consumer_sync();
-        if (tid == 0) s.carry += tot;
-    }
-    consumer_sync();
-    // this CTA's tiles, job by job (the escaped exponents of a job are counted into that job's histogram)
-    for (int j = 0; j < pa.n_jobs; ++j) {
-        const PackJob &jb = pa.job[j];
-        const bool do_hist = HIST && jb.hist != nullptr;
-        if (do_hist) {
-            for (int i = tid; i < kPWarps * 2 * 256; i += kConsumerThreads) warp_hist[i] = 0;
-            consumer_sync();
-        }
-        int *my_hist = warp_hist + (warp * 2 + (lane & 1)) * 256;
-        const int64_t job_end = jb.tile0 + (int64_t)jb.n_blocks * pa.BH;
-        const int job_base = jb.tile0 > 0 ? prefix[jb.tile0 - 1] : 0;
-        if (blockIdx.x == 0 && tid == 0) jb.seg_off[0] = 0;
-        // first tile of this CTA inside the job, then every gridDim.x-th; warp w takes every kPWarps-th of them
-        int64_t first = jb.tile0 + ((int64_t)blockIdx.x - jb.tile0 % gridDim.x + gridDim.x) % gridDim.x;
-        for (int64_t t = first + (int64_t)warp * gridDim.x; t < job_end; t += (int64_t)kPWarps * gridDim.x) {
-            const int incl = prefix[t];
-            const int c = incl - (t > 0 ? prefix[t - 1] : 0);
-            const int64_t gb = t / pa.BH;
-            const int blk_base = gb * pa.BH > 0 ? prefix[gb * pa.BH - 1] : 0;
-            if (lane == 0) {
-                jb.tile_base[t - jb.tile0] = incl - blk_base;
-                if ((t + 1) % pa.BH == 0) jb.seg_off[gb + 1 - jb.blk0] = (int64_t)(incl - job_base);
-            }
-            if (c != 0) compact_tile_units(pa, jb, t, (int64_t)(incl - c - job_base), c, my_hist, do_hist);
-        }
-        if (do_hist) {
-            consumer_sync();
-            if (tid < 256) {
-                int total = 0;
-#pragma unroll 4
-                for (int i = 0; i < kPWarps * 2; ++i) total += warp_hist[i * 256 + tid];
-                if (total != 0) atomicAdd(jb.hist + tid, total);
-            }
-            consumer_sync();
-        }
-    }
-}
-
 // Per-thread in-window counters (16-bit fields) -> the CTA's shared histogram.
 template <int N>
 __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::v], int left, int *s_hist) {
@@ -894,13 +791,9 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
         const bool valid = c < chunks;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
         if (valid) {
-            // 32 bytes per lane: lanes 4-7 of every eight load their halves in the opposite order, so
-            // that each 16-byte load instruction covers all banks once (see unpack_unit)
             const uint4 *p = reinterpret_cast<const uint4 *>(st.in + c * 16);
-            const bool flip = kSwizzleHalves && (lane & 4);
-            const uint4 a = p[flip ? 1 : 0], b = p[flip ? 0 : 1];
-            w0 = flip ? b : a;
-            w1 = flip ? a : b;
+            w0 = p[0];
+            w1 = p[1];
         }
         const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         uint32_t smw[4];
@@ -1098,34 +991,6 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
     bulk_wait_all();
     __threadfence();
     consumer_sync();
-    if (pa.fused_tail) {
-        // Grid-wide barrier of a cooperative launch (all CTAs are resident): arrive, then wait with a
-        // bound for the others.  A second counter tells the last CTA to leave when both can be cleared.
-        if (tid == 0) {
-            atomicAdd(pa.done, 1u);
-            uint32_t polls = 0;
-            while (*reinterpret_cast<volatile unsigned int *>(pa.done) < gridDim.x) {
-                __nanosleep(64);
-                if (++polls > pa.poll_limit) {
-                    atomicOr(pa.status, ADACODE_STATUS_TIMEOUT);
-                    break;
-                }
-            }
-            __threadfence();
-        }
-        consumer_sync();
-        fused_tail<HIST>(pa, s);
-        __threadfence();
-        consumer_sync();
-        if (tid == 0) {
-            const unsigned left_before = atomicAdd(pa.done + 1, 1u);
-            if (left_before == gridDim.x - 1) {
-                pa.done[0] = 0u;
-                pa.done[1] = 0u;
-            }
-        }
-        return;
-    }
     if (tid == 0) {
         const unsigned ticket = atomicAdd(pa.done, 1u);
         s.is_last = (ticket == gridDim.x - 1);

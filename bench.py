@@ -75,7 +75,7 @@ def workload_config(world: int) -> dict:
         'l2': 'per-rank working set of a step (inputs + planes) exceeds L2 many times over; all layers are packed '
               'before any is unpacked, so nothing is re-read from L2',
         'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs); launches of '
-                    'neighbouring layers alternate between two streams',
+                    'neighbouring layers rotate over three streams',
     }
 
 
@@ -388,13 +388,15 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     esc_base = esc_base.to(dev)
     n_elems = sum(x.numel() for ent in slots for x in ent['x'])
     tiles_per_launch = 2 * per * S4_HEADS * (half // BLOCK)
-    # launches of neighbouring layers alternate between two streams (each with its own pack scratch and
-    # unpack destination): the tail of one launch and the compaction pass overlap the next launch
-    worker = torch.cuda.Stream(dev)
-    lanes = (main, worker)
+    # launches of neighbouring layers rotate over a few streams (each with its own pack scratch and unpack
+    # destination): the tail of one launch and its compaction pass overlap the next launch
+    n_lanes_cfg = max(1, min(int(args.lanes), 4))
+    workers = [torch.cuda.Stream(dev) for _ in range(n_lanes_cfg - 1)]
+    lanes = (main, *workers)
     ws2 = [torch.zeros(L.adacode_pack_workspace_bytes(tiles_per_launch, BLOCK * S4_DIM), dtype=torch.uint8, device=dev)
            for _ in lanes]
-    fork, join = torch.cuda.Event(), torch.cuda.Event()
+    fork = torch.cuda.Event()
+    joins = [torch.cuda.Event() for _ in workers]
     hists = torch.zeros((n_layers, 2, 2, 256), dtype=torch.int32, device=dev)       # [layer][span][k/v]
     hists_red = torch.zeros((n_layers, 2, 256), dtype=torch.int32, device=dev)      # span B, summed over ranks
     params_dev = torch.zeros((n_layers * 2, 2), dtype=torch.int32, device=dev)
@@ -414,11 +416,13 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     def on_lanes(fn, n_lanes: int) -> None:
         if n_lanes > 1:
             fork.record(main)
-            worker.wait_event(fork)
+            for w in workers:
+                w.wait_event(fork)
         fn(n_lanes)
         if n_lanes > 1:
-            join.record(worker)
-            main.wait_event(join)
+            for w, j in zip(workers, joins):
+                j.record(w)
+                main.wait_event(j)
 
     def pack_layer(li: int, si: int = 0) -> None:
         ent = slots[li]
@@ -507,7 +511,7 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         hists.zero_()
         if ev:
             ev[0].record(main)
-        n_lanes = 1 if check is not None else 2
+        n_lanes = 1 if check is not None else len(lanes)
         on_lanes(lambda nl: [pack_layer(li, li % nl) for li in range(n_layers)], n_lanes)
         if ev:
             ev[1].record(main)
@@ -1391,6 +1395,7 @@ def main() -> None:
     ap.add_argument('--blocks', default='', help="comma list of main,config1,config3,config2 (default: all of them "
                                                  'on one GPU, main on several)')
     ap.add_argument('--layers', type=int, default=0, help='layers of the primary workload (default: all 36)')
+    ap.add_argument('--lanes', type=int, default=3, help='streams that the launches of neighbouring layers alternate between')
     ap.add_argument('--c2-batch', type=int, default=32)
     ap.add_argument('--c2-prompt', type=int, default=4096)
     ap.add_argument('--c2-new', type=int, default=128)

@@ -8,7 +8,7 @@ The reference has no compiled code; its pure-torch pack (``compress_open_tiled_r
 interpreter and is byte-identical to its Triton pack.  It handles one sequence and one 128-token
 block per call, so the sample is looped over sequences and blocks, as the reference's cache would.
 Its only unpack is a Triton kernel; one block is decoded under ``TRITON_INTERPRET=1`` for the
-record.  Prints one JSON line; the figures quoted in BASELINE.md come from this script.
+record.  Prints one JSON line.
 """
 from __future__ import annotations
 

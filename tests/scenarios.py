@@ -71,7 +71,7 @@ def _adj(**kw):
 
 
 SCENARIOS = {s.name: s for s in [
-    # BASELINE config 0: one 2048-token update of K,V [1, 8, 2048, 128]
+    # single-layer round trip: one 2048-token update of K,V [1, 8, 2048, 128]
     Scenario('config0_prefill_2048', 'float11', 1,
              dict(right=[(130, 129)], exp_bits=[(3, 3)], **_adj()),
              _kv_stream((1, 8, 128), (1, 8, 128), seed=0, prefill=2048, decode=0)),

@@ -232,3 +232,44 @@ def test_hf_decode_steps_with_fused_attention(cuda_device):
     assert abs(mp['kv_compressed_memory'] - mf['kv_compressed_memory']) <= 0.01 * mp['kv_compressed_memory']
     assert mf['materialize_calls'] == 0 and mp['materialize_calls'] > 0
     assert plain.layers[0].segment_params() == fused.layers[0].segment_params()      # layer 0 sees identical K/V
+
+
+def test_fused_hook_refuses_what_it_cannot_serve(cuda_device):
+    """The fused attention function attends to every cached token: a step whose mask hides cached
+    positions, a sliding-window layer, or a model left on another attention implementation must
+    raise instead of silently computing something else."""
+    from adacode_b200 import Float11Cache, hf_attention
+    from tests.scenarios import StubConfig
+    cache = Float11Cache(StubConfig(1), right=129, exp_bits=4, need_adjust=False, update_steps=0, block_size=128,
+                         layout='segmented_tiled')
+    k = synth.kv_tensor((2, 2, 200, 128), seed=61, key_offset=True).to(cuda_device)
+    v = synth.kv_tensor((2, 2, 200, 128), seed=62).to(cuda_device)
+    cache.update(k[:, :, :199], v[:, :, :199], 0)
+
+    class Layer:
+        layer_idx = 0
+        sliding_window = None
+
+    q = (torch.randn(2, 4, 1, 128, device=cuda_device) * 0.3).to(torch.bfloat16)
+    with hf_attention.fused_decode(cache):
+        cache.update(k[:, :, 199:], v[:, :, 199:], 0)
+        out, _ = hf_attention.float11_fused_attention(Layer(), q, None, None, None, scaling=128 ** -0.5)
+        assert out.shape == (2, 1, 4, 128)
+        visible = torch.zeros((2, 1, 1, 200), device=cuda_device)
+        out2, _ = hf_attention.float11_fused_attention(Layer(), q, None, None, visible, scaling=128 ** -0.5)
+        assert torch.equal(out, out2)                      # an all-visible additive mask is fine
+        padded = visible.clone()
+        padded[0, :, :, :7] = float('-inf')
+        with pytest.raises(NotImplementedError, match='hides'):
+            hf_attention.float11_fused_attention(Layer(), q, None, None, padded, scaling=128 ** -0.5)
+        windowed = Layer()
+        windowed.sliding_window = 64
+        with pytest.raises(NotImplementedError, match='sliding window'):
+            hf_attention.float11_fused_attention(windowed, q, None, None, None, scaling=128 ** -0.5)
+
+    class Cfg:
+        _attn_implementation = 'sdpa'
+
+    with pytest.raises(RuntimeError, match='float11_fused'):
+        with hf_attention.fused_decode(cache, Cfg()):
+            pass
