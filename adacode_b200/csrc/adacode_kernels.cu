@@ -684,15 +684,32 @@ int ensure_dynamic_smem(Kernel kernel, size_t bytes) {
 uint32_t g_poll_limit = kMaxPolls;
 int g_withhold_unit = -1;
 
+template <class G>
+int launch_unpack_geom(const UnpackJobsArgs &ja, cudaStream_t st) {
+    int rc = ensure_dynamic_smem(k_unpack_pipe<G>, sizeof(UnpackSmemT<G>));
+    if (rc != ADACODE_OK) return rc;
+    const int grid = grid_for(ja.tile0[ja.n_jobs], G::kCtasPerSm);
+    k_unpack_pipe<G><<<grid, G::kThreads, sizeof(UnpackSmemT<G>), st>>>(ja);
+    ADACODE_CUDA_TRY(cudaGetLastError());
+    return ADACODE_OK;
+}
+
+// ADACODE_UNPACK_GEOMETRY=wide keeps the unpack kernel on the 16-warp geometry (for comparisons)
+bool unpack_prefers_wide() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = getenv("ADACODE_UNPACK_GEOMETRY");
+        cached = (e && strcmp(e, "wide") == 0) ? 1 : 0;
+    }
+    return cached == 1;
+}
+
 int launch_unpack_pipe(UnpackJobsArgs &ja, cudaStream_t st) {
     ja.poll_limit = g_poll_limit;
     ja.withhold_unit = g_withhold_unit;
-    int rc = ensure_dynamic_smem(k_unpack_pipe, sizeof(UnpackSmem));
-    if (rc != ADACODE_OK) return rc;
-    const int grid = grid_for(ja.tile0[ja.n_jobs], 2);
-    k_unpack_pipe<<<grid, kPipeThreads, sizeof(UnpackSmem), st>>>(ja);
-    ADACODE_CUDA_TRY(cudaGetLastError());
-    return ADACODE_OK;
+    // a unit holds at least eight token rows: the narrow geometry takes head_dim up to 1024
+    const bool narrow = ja.job[0].D <= NarrowGeom::kUnit / 8 && !unpack_prefers_wide();
+    return narrow ? launch_unpack_geom<NarrowGeom>(ja, st) : launch_unpack_geom<WideGeom>(ja, st);
 }
 
 int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {

@@ -3,8 +3,12 @@
 // while the current unit is processed, and results leave through shared memory with bulk
 // stores.  Included by adacode_kernels.cu inside its anonymous namespace.
 //
-// One CTA = 16 consumer warps + 1 producer warp, persistent over tiles.  A "unit" is a run of
-// whole token rows of one tile, at most 16384 elements (a whole 128 x 128 tile).
+// One CTA = W consumer warps + 1 producer warp, persistent over tiles.  A "unit" is a run of
+// whole token rows of one tile, at most W x 1024 elements.  Two geometries are built: the wide one
+// (16 warps, units of a whole 128 x 128 tile, 2 CTAs per SM) for the pack kernel and the fused
+// attention kernel, the narrow one (8 warps, units of 8192 elements, 4 CTAs per SM) for the unpack
+// kernel, which measured 5-8 % faster with four smaller pipelines per SM than with two large ones
+// (the pack kernel measured 7 % slower that way: twice the escape slots and unit counts to compact).
 //   producer warp : waits for a free stage, issues the unit's bulk loads (sign/mantissa and
 //                   code planes, or source rows) against the stage's "full" mbarrier, and
 //                   stages the tile's escape bytes with plain loads
@@ -19,10 +23,24 @@
 #pragma once
 
 constexpr int kPCPT = 2;                                   // 16-element chunks per consumer thread and unit
-constexpr int kPWarps = 1024 / (32 * kPCPT);                // consumer warps
-constexpr int kConsumerThreads = kPWarps * 32;
-constexpr int kPipeThreads = kConsumerThreads + 32;
-constexpr int kUnitElems = 16384;
+
+template <int W, int CTAS>
+struct PipeGeom {
+    static constexpr int kWarps = W;                        // consumer warps
+    static constexpr int kConsumers = W * 32;
+    static constexpr int kThreads = kConsumers + 32;        // + the producer warp
+    static constexpr int kUnit = kConsumers * kPCPT * 16;   // elements per unit
+    static constexpr int kCtasPerSm = CTAS;
+    static constexpr int kEscStage = kUnit / 2;             // bytes of a tile's escape stream staged with a unit
+};
+using WideGeom = PipeGeom<16, 2>;
+using NarrowGeom = PipeGeom<8, 4>;
+
+// the wide geometry under the names the pack kernel and the attention kernel use
+constexpr int kPWarps = WideGeom::kWarps;
+constexpr int kConsumerThreads = WideGeom::kConsumers;
+constexpr int kPipeThreads = WideGeom::kThreads;
+constexpr int kUnitElems = WideGeom::kUnit;
 constexpr int kStages = 2;
 constexpr uint32_t kMaxPolls = 1u << 22;
 
@@ -82,7 +100,8 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // makes shared-memory writes of this thread visible to the async proxy (bulk stores)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+template <int THREADS = kConsumerThreads>
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
 // Inclusive warp scan of kPCPT per-lane counters walked in (k, lane) order (counters <= 16 each, so
 // they travel as 16-bit fields).  incl[k] = inclusive rank of (k, lane) within the warp's
@@ -119,25 +138,27 @@ __device__ __forceinline__ int warp_scan_counts(const int (&cnt)[kPCPT], int (&i
 
 // Exclusive prefix of this warp and the total over all consumer warps, from the per-warp totals
 // in shared memory: lane i reads warp i's total, one warp scan, two shuffles.
+template <int W = kPWarps>
 __device__ __forceinline__ void cross_warp_prefix(const int *warp_tot, int &prefix, int &total) {
-    static_assert(kPWarps <= 32, "one lane per consumer warp");
+    static_assert(W <= 32, "one lane per consumer warp");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int x = lane < kPWarps ? warp_tot[lane] : 0;
+    int x = lane < W ? warp_tot[lane] : 0;
 #pragma unroll
-    for (int d = 1; d < kPWarps; d <<= 1) {
+    for (int d = 1; d < W; d <<= 1) {
         const int u = __shfl_up_sync(kFull, x, d);
         if (lane >= d) x += u;
     }
-    total = __shfl_sync(kFull, x, kPWarps - 1);
+    total = __shfl_sync(kFull, x, W - 1);
     const int incl = __shfl_sync(kFull, x, warp);
-    const int own = __shfl_sync(kFull, lane < kPWarps ? warp_tot[lane] : 0, warp);
+    const int own = __shfl_sync(kFull, lane < W ? warp_tot[lane] : 0, warp);
     prefix = incl - own;
 }
 
 // Rows of one tile handled per unit: whole rows, a multiple of 8 (so that code bytes per unit are a
-// multiple of 16), at most kUnitElems elements.
+// multiple of 16), at most UNIT elements (D <= UNIT / 8).
+template <int UNIT = kUnitElems>
 __host__ __device__ inline int unit_rows_for(int seq_tile, int D) {
-    int r = (kUnitElems / D) & ~7;
+    int r = (UNIT / D) & ~7;
     if (r < 8) r = 8;
     return r < seq_tile ? r : seq_tile;
 }
@@ -146,7 +167,7 @@ __host__ __device__ inline int unit_rows_for(int seq_tile, int D) {
 // unpack
 // ---------------------------------------------------------------------------------------
 
-constexpr int kEscStage = 8192;   // bytes of a tile's escape stream staged in shared memory
+constexpr int kEscStage = WideGeom::kEscStage;
 
 struct UnitMeta {
     uint16_t *dst;            // first element of the unit in the destination
@@ -163,22 +184,26 @@ struct UnitMeta {
 };
 
 // bulk copies need 16-byte aligned shared addresses: every buffer starts on a 128-byte boundary
-struct alignas(128) UnpackStage {
-    alignas(128) uint8_t sm[kUnitElems];
-    alignas(128) uint8_t codes[kUnitElems / 2];
-    alignas(128) uint8_t esc[kEscStage + 16];
+template <class G>
+struct alignas(128) UnpackStageT {
+    alignas(128) uint8_t sm[G::kUnit];
+    alignas(128) uint8_t codes[G::kUnit / 2];
+    alignas(128) uint8_t esc[G::kEscStage + 16];
     alignas(16) UnitMeta meta;
 };
 
-struct alignas(128) UnpackSmem {
-    UnpackStage stage[kStages];
-    alignas(128) uint16_t out[kUnitElems];
+template <class G>
+struct alignas(128) UnpackSmemT {
+    UnpackStageT<G> stage[kStages];
+    alignas(128) uint16_t out[G::kUnit];
     alignas(16) uint32_t lut[1024];   // decode table of the current (left, nbits)
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
-    int warp_tot[kPWarps];
+    int warp_tot[G::kWarps];
 };
-static_assert(sizeof(UnpackStage) % 128 == 0, "stage buffers must stay 128-byte aligned");
+using UnpackStage = UnpackStageT<WideGeom>;
+static_assert(sizeof(UnpackStageT<WideGeom>) % 128 == 0 && sizeof(UnpackStageT<NarrowGeom>) % 128 == 0,
+              "stage buffers must stay 128-byte aligned");
 
 struct UnpackPipeArgs {
     // uniform form (seg == nullptr): planes as adacode_pack_tiles wrote them
@@ -273,12 +298,13 @@ struct EscWindow {
     int win, tail, staged, shift;
 };
 
+template <int ESC_STAGE = kEscStage>
 __device__ __forceinline__ EscWindow esc_window(const TileSrc &t) {
     EscWindow w;
     // stage no more than the stream really holds, so that a short stream is reported as such
     long long avail = t.esc_len - t.esc_start;
     if (avail > t.esc_cnt) avail = t.esc_cnt;
-    if (avail > kEscStage) avail = kEscStage;
+    if (avail > ESC_STAGE) avail = ESC_STAGE;
     w.staged = avail > 0 ? (int)avail : 0;
     const uint8_t *ea = t.esc + t.esc_start;
     w.shift = (int)((uintptr_t)ea & 15);
@@ -296,7 +322,8 @@ __device__ __forceinline__ EscWindow esc_window(const TileSrc &t) {
 
 // Producer warp, stage known to be free: describe the unit (rows [row0, row0 + rows) of tile t) in
 // the stage's meta block and start its bulk copies against `full_bar`.
-__device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, const TileSrc &t, const EscWindow &w,
+template <class Stage>
+__device__ __forceinline__ void issue_unit(Stage &st, uint64_t *full_bar, const TileSrc &t, const EscWindow &w,
                                            int row0, int rows, int D, uint16_t *dst, bool first_unit,
                                            int32_t *status, bool withhold = false) {
     const int lane = threadIdx.x & 31;
@@ -341,8 +368,8 @@ __device__ __forceinline__ void issue_unit(UnpackStage &st, uint64_t *full_bar, 
 // consumer thread decodes its kPCPT chunks of the staged planes into registers (exponent fields
 // from the table, 0 where the code is 0; sign and mantissa merged in) and notes where the
 // escapes are (zm: one bit per code-0 slot of each group word; zc: their number per chunk).
-template <int N>
-__device__ __forceinline__ void decode_chunks(const UnpackStage &st, const uint32_t *lut, int chunks,
+template <int N, class Stage>
+__device__ __forceinline__ void decode_chunks(const Stage &st, const uint32_t *lut, int chunks,
                                               uint4 (&o)[kPCPT][2], uint32_t (&zm)[kPCPT][2], int (&zc)[kPCPT]) {
     constexpr int CB = 2 * N;   // code bytes per 16-element chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -374,8 +401,8 @@ __device__ __forceinline__ void decode_chunks(const UnpackStage &st, const uint3
     }
 }
 
-template <int N>
-__device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st, uint64_t *empty_bar,
+template <int N, class G>
+__device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStageT<G> &st, uint64_t *empty_bar,
                                             int &consumed, int D, int32_t *status) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const UnitMeta m = st.meta;
@@ -392,9 +419,9 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;
     bulk_wait_read();          // the previous unit's store has finished reading s.out
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     int wprefix, unit_tot;
-    cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+    cross_warp_prefix<G::kWarps>(s.warp_tot, wprefix, unit_tot);
     static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
     const int c0 = warp * (kPCPT * 32) + lane;
 #pragma unroll
@@ -458,7 +485,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
     consumed += unit_tot;
     mbar_arrive(empty_bar);    // this thread no longer reads the stage
     fence_async_smem();
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     if (rows_contig) {
         if (tid == 0 && m.elems > 0) {
             bulk_store(m.dst, s.out, (uint32_t)m.elems * 2u);
@@ -466,7 +493,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmem &s, const UnpackStage &st
         }
     } else {
         const int rows = m.elems / D;
-        for (int r = tid; r < rows; r += kConsumerThreads) bulk_store(m.dst + (long long)r * ds, s.out + r * D, (uint32_t)D * 2u);
+        for (int r = tid; r < rows; r += G::kConsumers) bulk_store(m.dst + (long long)r * ds, s.out + r * D, (uint32_t)D * 2u);
         bulk_commit();
     }
 }
@@ -482,9 +509,10 @@ struct UnpackJobsArgs {
     int withhold_unit;        // testing aid: CTA 0's producer never signals this unit as loaded (-1: off)
 };
 
-__global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const __grid_constant__ UnpackJobsArgs ja) {
+template <class G>
+__global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(const __grid_constant__ UnpackJobsArgs ja) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    UnpackSmem &s = *reinterpret_cast<UnpackSmem *>(smem_raw);
+    UnpackSmemT<G> &s = *reinterpret_cast<UnpackSmemT<G> *>(smem_raw);
     const int tid = threadIdx.x;
     const UnpackPipeArgs &a0 = ja.job[0];          // geometry and status word are common to all jobs
     const long long n_tiles = ja.tile0[ja.n_jobs];
@@ -492,16 +520,16 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const __grid_co
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], kConsumerThreads);
+            mbar_init(&s.empty[i], G::kConsumers);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    const int unit_rows = unit_rows_for(a0.seq_tile, a0.D);
+    const int unit_rows = unit_rows_for<G::kUnit>(a0.seq_tile, a0.D);
     const int units_per_tile = (a0.seq_tile + unit_rows - 1) / unit_rows;
 
-    if (tid >= kConsumerThreads) {
+    if (tid >= G::kConsumers) {
         // ---------------- producer warp ----------------
         // Tile metadata sits behind two dependent global loads (segment record, then the tile's
         // escape range).  Each lane resolves one of this CTA's next 32 tiles, so those round trips
@@ -521,7 +549,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const __grid_co
             const int n_here = (int)(my_tiles - base < 32 ? my_tiles - base : 32);
             for (int j = 0; j < n_here; ++j) {
                 const TileSrc t = shfl_tile(mine, j);
-                const EscWindow w = esc_window(t);
+                const EscWindow w = esc_window<G::kEscStage>(t);
                 for (int u = 0; u < units_per_tile; ++u, ++it) {
                     const int stg = it % kStages;
                     mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a0.status, ja.poll_limit);
@@ -550,14 +578,14 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_unpack_pipe(const __grid_co
             const int stg = it % kStages;
             if ((tid & 31) == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, a0.status, ja.poll_limit);
             __syncwarp();
-            const UnpackStage &st = s.stage[stg];
+            const UnpackStageT<G> &st = s.stage[stg];
             const int nb = st.meta.nbits, lf = st.meta.left;
             if (nb != lut_nbits || lf != lut_left) {
                 // uniform over the CTA: every consumer read the same meta.  The previous unit ended
                 // with a consumer barrier, so nobody still reads the old table.
-                build_decode_lut(s.lut, nb, lf, kConsumerThreads);
+                build_decode_lut(s.lut, nb, lf, G::kConsumers);
                 lut_nbits = nb, lut_left = lf;
-                consumer_sync();
+                consumer_sync<G::kConsumers>();
             }
             switch (nb) {
                 case 1: unpack_unit<1>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;

@@ -38,6 +38,7 @@ from .codec import SegmentRef, TiledCompressedTensor
 
 _SUPPORTED_LAYOUTS = ('segmented_tiled', 'legacy', 'tiled')
 _LEGACY_BLOCK_GAPS = (8, 4, 8, 2)      # escape-base blocks of the flat layout: 128 x gap elements
+_MAX_LAUNCH_ELEMS = 2 ** 31 - 1         # one pack launch (keys and values together) stays below this
 
 
 def _segmented_state(segment_states: list) -> Optional[dict]:
@@ -387,7 +388,7 @@ class float11Layer(DynamicLayer):
         # packed in several launches, block range by block range.
         B, H, S, D = key_states.shape
         per_block = max(int(B * H * self.seq_tile_size * max(D, value_states.shape[-1])), 1)
-        blocks_per_call = max(1, (2 ** 31 - 1) // (2 * per_block))
+        blocks_per_call = max(1, _MAX_LAUNCH_ELEMS // (2 * per_block))
         total_blocks = S // self.seq_tile_size
         k_hist = v_hist = kh_host = vh_host = None
         for b_lo in range(0, total_blocks, blocks_per_call):

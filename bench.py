@@ -606,7 +606,12 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         windows_agree = bool(torch.equal(lo, hi))
 
     # ---- reduced replica through the cache API, sharded over the NCCL ranks, against the oracle ----
-    replica = replica_parity(dev, world, rank)
+    # (sigma x2 as the configuration says, which this data's adjuster answers by keeping its window in
+    # most tensors, and x16, which makes it move)
+    replica = replica_parity(dev, world, rank, shift_scale=16.0)
+    replica_x2 = replica_parity(dev, world, rank, shift_scale=2.0)
+    replica['ok'] = replica['ok'] and replica_x2['ok']
+    replica['detail'] = {'sigma_x16': replica['detail'], 'sigma_x2': replica_x2['detail']}
 
     # ---- end to end through the public API with host buffers ----------------------------
     e2e = e2e_leg(args, dev, world, rank, slots, calib, per, b0)
@@ -680,13 +685,13 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     }
     if world == 1:
         spans = cpu_sample()
-        cpu_dt, cpu_n, cpu_threads = cpu_round_trip(spans, repeats=2)
+        cpu_dt, cpu_n, cpu_threads = cpu_round_trip(spans, repeats=10)
         line['cpu_baseline'] = {'value': round(2 * 2 * cpu_n / cpu_dt / 1e9, 3), 'unit': 'GB/s', 'cores': cpu_threads,
                                 'kind': 'port', 'sample': CPU_SAMPLE_TEXT}
     return line
 
 
-def replica_parity(dev, world: int, rank: int) -> dict:
+def replica_parity(dev, world: int, rank: int, shift_scale: float = 16.0) -> dict:
     """A reduced replica of the stress schedule through the product's sharded path: every rank runs
     Float11Cache(hist_reduce=all-reduce over the ranks) on its sequences -- a 512-token prefill, then
     single-token appends with sigma doubled for heads 4-7, so that blocks are staged exactly on adjust
@@ -718,7 +723,7 @@ def replica_parity(dev, world: int, rank: int) -> dict:
         sigma, offset = tabs[(l, wi)]
         right, nbits = calib[(l, wi)]
         return kv_synth.kv_tensor(800 + 2 * l + wi, (nb, H, total, D), sigma, offset, device, b0=b_start,
-                                  shift_from=shift, shift_heads=S4_SHIFT_HEADS, shift_scale=16.0,
+                                  shift_from=shift, shift_heads=S4_SHIFT_HEADS, shift_scale=shift_scale,
                                   escapes=(right - 2 ** nbits + 1, right, S4_P_WINDOW, S4_P_ZERO))
 
     for l in range(n_layers):
@@ -752,7 +757,7 @@ def replica_parity(dev, world: int, rank: int) -> dict:
         gathered = [None] * world if rank == 0 else None
         dist.gather_object(mine, gathered, dst=0)
     detail = {'schedule': f'{n_layers} layers, {per} sequences per rank, {prefill}-token prefill + {appends} single-token '
-                          'appends, sigma x16 for heads 4-7 from the first appended token',
+                          f'appends, sigma x{shift_scale:g} for heads 4-7 from the first appended token',
               'ranks': world}
     if rank != 0:
         return {'ok': ok, 'detail': detail}

@@ -235,3 +235,23 @@ def test_runner_writes_reference_shaped_records(cuda_device, tmp_path, monkeypat
     assert 0.6 < f11['kv_compressed_memory'] / f11['kv_original_memory'] < 1.0
     with pytest.raises(NotImplementedError):
         runner.run(runner.get_parse().parse_args(common + ['--kv_cache_impl', 'nvcomp_ans']))
+
+
+def test_long_prefill_is_packed_in_several_launches(cuda_device, monkeypatch):
+    """A prefill whose keys and values together would exceed the per-launch element limit is packed
+    block range by block range; the cache ends in exactly the state of a single launch."""
+    import adacode_b200.float_cache_utils as fc
+    from adacode_b200 import Float11Cache
+    k = synth.kv_tensor((2, 2, 128 * 7 + 30, 64), seed=71, key_offset=True).to(cuda_device)
+    v = synth.kv_tensor((2, 2, 128 * 7 + 30, 64), seed=72).to(cuda_device)
+    kw = dict(right=[(129, 128)], exp_bits=[(3, 3)], need_adjust=True, update_steps=128, block_size=128,
+              layout='segmented_tiled')
+    digests = []
+    for limit in (2 ** 31 - 1, 2 * 3 * (2 * 2 * 128 * 64)):            # the second: three blocks per launch
+        monkeypatch.setattr(fc, '_MAX_LAUNCH_ELEMS', limit)
+        cache = Float11Cache(scenarios.StubConfig(1), **kw)
+        cache.update(k, v, 0)
+        dk, dv = cache.update(k[:, :, :1], v[:, :, :1], 0)               # applies the prefill's adjust proposal
+        assert torch.equal(dk[:, :, :-1], k) and torch.equal(dv[:, :, :-1], v)
+        digests.append(scenarios.layer_digest(cache.layers[0]))
+    assert digests[0] == digests[1] and len(digests[0]['key_segments']) == 7

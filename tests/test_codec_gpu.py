@@ -33,7 +33,8 @@ def _check_chunk_against_oracle(chunk, hist, x_cpu, right, nbits, seq_tile):
 
 
 @pytest.mark.parametrize('nbits', [1, 2, 3, 4])
-@pytest.mark.parametrize('shape', [(1, 8, 128, 128), (3, 2, 256, 64), (2, 1, 128, 512), (1, 2, 128, 72), (2, 3, 384, 16)])
+@pytest.mark.parametrize('shape', [(1, 8, 128, 128), (3, 2, 256, 64), (2, 1, 128, 512), (1, 2, 128, 72), (2, 3, 384, 16),
+                                   (1, 2, 128, 1024), (1, 1, 128, 1040), (1, 1, 128, 2048)])
 def test_pack_matches_oracle_and_round_trips(cuda_device, nbits, shape):
     from adacode_b200 import codec
     x_cpu = synth.kv_tensor(shape, seed=7 + nbits, key_offset=True)
