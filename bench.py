@@ -614,7 +614,15 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     replica['detail'] = {'sigma_x16': replica['detail'], 'sigma_x2': replica_x2['detail']}
 
     # ---- end to end through the public API with host buffers ----------------------------
-    e2e = e2e_leg(args, dev, world, rank, slots, calib, per, b0)
+    def release_workload():
+        # the end-to-end leg needs the device memory that the resident workload holds
+        nonlocal out, ent, x
+        out = ent = x = None
+        for held in (slots, out2, ws2):
+            held.clear()
+        torch.cuda.empty_cache()
+
+    e2e = e2e_leg(args, dev, world, rank, slots, calib, per, b0, release_workload)
 
     stats = torch.tensor([total_ms, pack_ms, unpack_ms, table_ms, e2e['ms'], e2e['copy_ms'],
                           0.0 if round_trip_ok else 1.0, 0.0 if replica['ok'] else 1.0], dtype=torch.float64, device=dev)
@@ -792,16 +800,16 @@ def replica_parity(dev, world: int, rank: int, shift_scale: float = 16.0) -> dic
     return {'ok': ok and not bad, 'detail': detail}
 
 
-def e2e_leg(args, dev, world: int, rank: int, slots, calib, per: int, b0: int) -> dict:
+def e2e_leg(args, dev, world: int, rank: int, slots, calib, per: int, b0: int, release_workload) -> dict:
     """Host K/V -> device -> Float11Cache.update (pack) -> materialize_layer (unpack) -> host, on the
-    first few layers of the workload (as many as give about 4 GB of K+V per rank); the copies of
+    first few layers of the workload (as many as give about ``--e2e-gb`` of K+V per rank); the copies of
     neighbouring layers run on their own streams.  Also a copy-only pass over the same buffers: the
     host<->device ceiling at this N."""
     import torch
     from adacode_b200 import Float11Cache
     main = torch.cuda.current_stream(dev)
     layer_bytes = 2 * slots[0]['x'][0].numel() * 2
-    n_l = max(2, min(len(slots), int(4.3e9 // layer_bytes)))
+    n_l = max(2, min(len(slots), int(args.e2e_gb * 1e9 // layer_bytes)))
     n_l = min(n_l, len(slots))
     cfg = StubConfig(n_l)
     rights = [(calib[(l, 'k')][0], calib[(l, 'v')][0]) for l in range(n_l)]
@@ -809,7 +817,9 @@ def e2e_leg(args, dev, world: int, rank: int, slots, calib, per: int, b0: int) -
     host_in = [[x.to('cpu').pin_memory() for x in slots[l]['x']] for l in range(n_l)]
     host_out = [torch.empty_like(host_in[0][0]).pin_memory() for _ in range(2)]
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    stage = [[torch.empty_like(slots[0]['x'][0]) for _ in range(2)] for _ in range(2)]      # double-buffered K, V
+    shape = tuple(slots[0]['x'][0].shape)
+    release_workload()
+    stage = [[torch.empty(shape, dtype=torch.bfloat16, device=dev) for _ in range(2)] for _ in range(2)]   # double-buffered K, V
     steps = max(1, min(args.steps, 3))
 
     def run(with_codec: bool):
@@ -1400,6 +1410,7 @@ def main() -> None:
     ap.add_argument('--blocks', default='', help="comma list of main,config1,config3,config2 (default: all of them "
                                                  'on one GPU, main on several)')
     ap.add_argument('--layers', type=int, default=0, help='layers of the primary workload (default: all 36)')
+    ap.add_argument('--e2e-gb', type=float, default=17.2, help='K+V bytes per rank that one pass of the end-to-end leg moves (GB)')
     ap.add_argument('--lanes', type=int, default=3, help='streams that the launches of neighbouring layers alternate between')
     ap.add_argument('--c2-batch', type=int, default=32)
     ap.add_argument('--c2-prompt', type=int, default=4096)
