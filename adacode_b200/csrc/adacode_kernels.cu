@@ -720,24 +720,41 @@ int launch_unpack_pipe(const UnpackPipeArgs &a, cudaStream_t st) {
     return launch_unpack_pipe(ja, st);
 }
 
-template <typename Kernel>
-int launch_pack_kernel(Kernel kernel, const PackPipeArgs &pa, int grid, cudaStream_t st) {
-    int rc = ensure_dynamic_smem(kernel, sizeof(PackSmem));
+template <class G, typename Kernel>
+int launch_pack_kernel(Kernel kernel, const PackPipeArgs &pa, cudaStream_t st) {
+    int rc = ensure_dynamic_smem(kernel, sizeof(PackSmemT<G>));
     if (rc != ADACODE_OK) return rc;
-    kernel<<<grid, kPipeThreads, sizeof(PackSmem), st>>>(pa);
+    kernel<<<grid_for(pa.n_tiles, G::kCtasPerSm), G::kThreads, sizeof(PackSmemT<G>), st>>>(pa);
     ADACODE_CUDA_TRY(cudaGetLastError());
     return ADACODE_OK;
 }
 
-template <int N>
+template <int N, class G>
 int launch_pack_pipe_n(const PackPipeArgs &pa, bool hist, cudaStream_t st) {
-    const int grid = grid_for(pa.n_tiles, 2);
-    return hist ? launch_pack_kernel(k_pack_pipe<N, true>, pa, grid, st)
-                : launch_pack_kernel(k_pack_pipe<N, false>, pa, grid, st);
+    return hist ? launch_pack_kernel<G>(k_pack_pipe<N, true, G>, pa, st)
+                : launch_pack_kernel<G>(k_pack_pipe<N, false, G>, pa, st);
+}
+
+// The pack kernel takes the narrow geometry where a unit of the wide one would stay half empty
+// (tiles of at most 8192 elements, e.g. 128 tokens of a 64-wide head).
+// ADACODE_PACK_GEOMETRY=wide|narrow overrides the choice where the shape allows it (for comparisons).
+bool pack_takes_narrow(int seq_tile, int D) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *e = getenv("ADACODE_PACK_GEOMETRY");
+        forced = !e ? 0 : strcmp(e, "wide") == 0 ? 1 : strcmp(e, "narrow") == 0 ? 2 : 0;
+    }
+    if (D > NarrowGeom::kUnit / 8) return false;      // a unit holds at least eight token rows
+    if (forced != 0) return forced == 2;
+    return unit_rows_for<WideGeom::kUnit>(seq_tile, D) * D <= NarrowGeom::kUnit;
 }
 
 // Pipelined pack of all jobs of `pa` with one pack launch and one compaction launch.
 int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
+    const bool narrow = pack_takes_narrow(pa.seq_tile, pa.D);
+    pa.unit_rows = narrow ? unit_rows_for<NarrowGeom::kUnit>(pa.seq_tile, pa.D)
+                          : unit_rows_for<WideGeom::kUnit>(pa.seq_tile, pa.D);
+    pa.units_per_tile = (pa.seq_tile + pa.unit_rows - 1) / pa.unit_rows;
     bool hist = false;
     int max_blocks = 0;
     for (int j = 0; j < pa.n_jobs; ++j) {
@@ -745,11 +762,15 @@ int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
         max_blocks = pa.job[j].n_blocks > max_blocks ? pa.job[j].n_blocks : max_blocks;
     }
     int rc;
-    switch (nbits) {
-        case 1: rc = launch_pack_pipe_n<1>(pa, hist, st); break;
-        case 2: rc = launch_pack_pipe_n<2>(pa, hist, st); break;
-        case 3: rc = launch_pack_pipe_n<3>(pa, hist, st); break;
-        default: rc = launch_pack_pipe_n<4>(pa, hist, st); break;
+    switch (nbits + (narrow ? 4 : 0)) {
+        case 1: rc = launch_pack_pipe_n<1, WideGeom>(pa, hist, st); break;
+        case 2: rc = launch_pack_pipe_n<2, WideGeom>(pa, hist, st); break;
+        case 3: rc = launch_pack_pipe_n<3, WideGeom>(pa, hist, st); break;
+        case 4: rc = launch_pack_pipe_n<4, WideGeom>(pa, hist, st); break;
+        case 5: rc = launch_pack_pipe_n<1, NarrowGeom>(pa, hist, st); break;
+        case 6: rc = launch_pack_pipe_n<2, NarrowGeom>(pa, hist, st); break;
+        case 7: rc = launch_pack_pipe_n<3, NarrowGeom>(pa, hist, st); break;
+        default: rc = launch_pack_pipe_n<4, NarrowGeom>(pa, hist, st); break;
     }
     if (rc != ADACODE_OK) return rc;
     // one warp per tile; few enough CTAs that the final per-bin atomics of the histogram stay cheap
@@ -931,8 +952,6 @@ int pack_jobs_impl(const adacode_pack_job *jobs, int n_jobs, int B, int H, int s
         pa.n_tiles = n_tiles;
         pa.esc_scratch = sc.esc, pa.tile_counts = sc.tile_counts, pa.unit_counts = sc.unit_counts;
         pa.blk_off = sc.blk_off, pa.done = sc.done;
-        pa.unit_rows = unit_rows_for(seq_tile, D);
-        pa.units_per_tile = (seq_tile + pa.unit_rows - 1) / pa.unit_rows;
         pa.status = status;
         pa.poll_limit = g_poll_limit;
         return launch_pack_pipe(pa, nbits, st);

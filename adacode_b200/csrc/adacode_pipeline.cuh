@@ -651,7 +651,6 @@ __device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], ui
     }
 }
 
-constexpr int kPackEscStage = kUnitElems;   // worst case: every element of a unit escapes
 
 struct PackUnitMeta {
     uint8_t *sm_dst;       // sign/mantissa bytes of the unit
@@ -665,26 +664,29 @@ struct PackUnitMeta {
     int job;               // index into PackPipeArgs::job
 };
 
-struct alignas(128) PackStage {
-    alignas(128) uint16_t in[kUnitElems];
+template <class G>
+struct alignas(128) PackStageT {
+    alignas(128) uint16_t in[G::kUnit];
     alignas(16) PackUnitMeta meta;
 };
 
-struct alignas(128) PackSmem {
-    PackStage stage[kStages];
-    alignas(128) uint8_t sm[kUnitElems];
-    alignas(128) uint8_t codes[kUnitElems / 2];
-    alignas(128) uint8_t esc[kPackEscStage];
+template <class G>
+struct alignas(128) PackSmemT {
+    PackStageT<G> stage[kStages];
+    alignas(128) uint8_t sm[G::kUnit];
+    alignas(128) uint8_t codes[G::kUnit / 2];
+    alignas(128) uint8_t esc[G::kUnit];      // worst case: every element of a unit escapes
     alignas(16) uint8_t lut[256];      // exponent -> code (0 = outside the window)
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
-    int warp_tot[kPWarps];
+    int warp_tot[G::kWarps];
     int hist[256];
     int is_last;
     long long carry;
-    int scan[kPWarps];
+    int scan[G::kWarps];
 };
-static_assert(sizeof(PackStage) % 128 == 0, "stage buffers must stay 128-byte aligned");
+static_assert(sizeof(PackStageT<WideGeom>) % 128 == 0 && sizeof(PackStageT<NarrowGeom>) % 128 == 0,
+              "stage buffers must stay 128-byte aligned");
 
 // One tensor of a pack launch.  All jobs of a launch share B, H, seq_tile, D and the code length;
 // job j owns the global tiles [tile0, tile0 + BH * n_blocks) and the global blocks [blk0, blk0 + n_blocks).
@@ -724,10 +726,11 @@ __device__ __forceinline__ int job_of_tile(const PackPipeArgs &pa, int64_t tile)
 // Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets (per job).
 // Run by the consumer threads of the CTA that finished last, while the rest of the GPU is idle,
 // so it is kept short: every thread takes a run of kScanRun consecutive tiles, fetches their
-// counts with independent loads (one memory round trip per pass of 512 x kScanRun tiles), and
+// counts with independent loads (one memory round trip per pass of threads x kScanRun tiles), and
 // one block scan of the run totals gives every tile its prefix.
 constexpr int kScanRun = 8;
 
+template <class G>
 __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long long *s_carry, int *s_scan) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -735,8 +738,8 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
         pa.blk_off[0] = 0;
     }
     if (tid < pa.n_jobs) pa.job[tid].seg_off[0] = 0;
-    consumer_sync();
-    const int64_t per_pass = (int64_t)kConsumerThreads * kScanRun;
+    consumer_sync<G::kConsumers>();
+    const int64_t per_pass = (int64_t)G::kConsumers * kScanRun;
     for (int64_t pass = 0; pass < pa.n_tiles; pass += per_pass) {
         const int64_t t0 = pass + (int64_t)tid * kScanRun;
         int c[kScanRun];
@@ -752,10 +755,10 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
             if (lane >= d) x += u;
         }
         if (lane == 31) s_scan[warp] = x;
-        consumer_sync();
+        consumer_sync<G::kConsumers>();
         int wp = 0, tot = 0;
 #pragma unroll
-        for (int i = 0; i < kPWarps; ++i) {
+        for (int i = 0; i < G::kWarps; ++i) {
             const int v = s_scan[i];
             wp += (i < warp) ? v : 0;
             tot += v;
@@ -769,7 +772,7 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
             inc[i] = incl;                                // inclusive prefix over the whole launch
             if (t < pa.n_tiles && (t + 1) % pa.BH == 0) pa.blk_off[(t + 1) / pa.BH] = incl;
         }
-        consumer_sync();                                  // block offsets up to the end of this pass are written
+        consumer_sync<G::kConsumers>();                                  // block offsets up to the end of this pass are written
         if (tid == 0) *s_carry += tot;
 #pragma unroll
         for (int i = 0; i < kScanRun; ++i) {
@@ -781,7 +784,7 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
                 if ((t + 1) % pa.BH == 0) jb.seg_off[gb + 1 - jb.blk0] = inc[i] - pa.blk_off[jb.blk0];
             }
         }
-        consumer_sync();
+        consumer_sync<G::kConsumers>();
     }
     if (tid == 0) *pa.done = 0u;
 }
@@ -801,8 +804,8 @@ __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::
     for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
 }
 
-template <int N, bool HIST>
-__device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint64_t *empty_bar,
+template <int N, bool HIST, class G>
+__device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &st, uint64_t *empty_bar,
                                           int &running, uint32_t (&cnt2)[HistRegs<N>::v]) {
     constexpr int CB = 2 * N;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -853,9 +856,9 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
     const int wtot = warp_scan_counts(zc, incl);
     if (lane == 0) s.warp_tot[warp] = wtot;
     bulk_wait_read();      // the previous unit's stores have finished reading the out buffers
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     int wprefix, unit_tot;
-    cross_warp_prefix(s.warp_tot, wprefix, unit_tot);
+    cross_warp_prefix<G::kWarps>(s.warp_tot, wprefix, unit_tot);
     static_assert(kPCPT == 2, "the escape loop below walks the two chunks of a thread together");
     const int c0 = warp * (kPCPT * 32) + lane;
 #pragma unroll
@@ -887,7 +890,7 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
     }
     mbar_arrive(empty_bar);
     fence_async_smem();
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     running += unit_tot;
     if (tid == 0) {
         if (m.elems > 0) {
@@ -901,16 +904,17 @@ __device__ __forceinline__ void pack_unit(PackSmem &s, const PackStage &st, uint
     }
 }
 
-template <int N, bool HIST>
-__global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_constant__ PackPipeArgs pa) {
+template <int N, bool HIST, class G>
+__global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const __grid_constant__ PackPipeArgs pa) {
+    static_assert(G::kConsumers >= 256, "the 256-entry tables are filled by one consumer thread per entry");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    PackSmem &s = *reinterpret_cast<PackSmem *>(smem_raw);
+    PackSmemT<G> &s = *reinterpret_cast<PackSmemT<G> *>(smem_raw);
     const int tid = threadIdx.x;
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], kConsumerThreads);
+            mbar_init(&s.empty[i], G::kConsumers);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -919,7 +923,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
 
     const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
 
-    if (tid >= kConsumerThreads) {
+    if (tid >= G::kConsumers) {
         // ---------------- producer warp ----------------
         const int lane = tid & 31;
         uint32_t it = 0;
@@ -934,7 +938,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
             const bool rows_contig = (jb.ss == pa.D);
             for (int u = 0; u < upt; ++u, ++it) {
                 const int stg = it % kStages;
-                PackStage &st = s.stage[stg];
+                PackStageT<G> &st = s.stage[stg];
                 mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, pa.status, pa.poll_limit);
                 const int row0 = u * unit_rows;
                 const int rows = min(unit_rows, pa.seq_tile - row0);
@@ -989,7 +993,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
                 // job's histogram over and build the new job's code table.  The previous unit ended with
                 // a consumer barrier, so nobody still encodes with the old table.
                 if (HIST && cur_job >= 0) flush_code_counts<N>(cnt2, cur_left, s.hist);
-                consumer_sync();
+                consumer_sync<G::kConsumers>();
                 if (HIST && cur_job >= 0 && tid < 256) {
                     const int hv = s.hist[tid];
                     if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
@@ -1001,16 +1005,16 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
                     const uint32_t code = (uint32_t)tid - (uint32_t)cur_left;
                     s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
                 }
-                consumer_sync();
+                consumer_sync<G::kConsumers>();
             }
-            pack_unit<N, HIST>(s, s.stage[stg], &s.empty[stg], running, cnt2);
+            pack_unit<N, HIST, G>(s, s.stage[stg], &s.empty[stg], running, cnt2);
             // the per-thread counters are 16-bit fields and grow by at most 32 per unit
             if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
         }
     }
     if (HIST && cur_job >= 0) {
         flush_code_counts<N>(cnt2, cur_left, s.hist);
-        consumer_sync();
+        consumer_sync<G::kConsumers>();
         if (tid < 256) {
             const int hv = s.hist[tid];
             if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
@@ -1018,15 +1022,15 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_pack_pipe(const __grid_cons
     }
     bulk_wait_all();
     __threadfence();
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     if (tid == 0) {
         const unsigned ticket = atomicAdd(pa.done, 1u);
         s.is_last = (ticket == gridDim.x - 1);
     }
-    consumer_sync();
+    consumer_sync<G::kConsumers>();
     if (!s.is_last) return;
     __threadfence();
-    scan_tile_counts(pa, &s.carry, s.scan);
+    scan_tile_counts<G>(pa, &s.carry, s.scan);
 }
 
 // One warp copies the escape bytes of tile t (its units follow each other in the scratch) to `dst`
