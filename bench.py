@@ -74,7 +74,8 @@ def workload_config(world: int) -> dict:
         'sequences_per_gpu': S4_BATCH // world, 'block_size': BLOCK,
         'l2': 'per-rank working set of a step (inputs + planes) exceeds L2 many times over; all layers are packed '
               'before any is unpacked, so nothing is re-read from L2',
-        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs); launches of '
+        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs; both spans of a layer '
+                    'where four tensors stay below 2**31 elements, i.e. from two GPUs up); launches of '
                     'neighbouring layers rotate over three streams',
     }
 
@@ -387,7 +388,9 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         slots.append(ent)
     esc_base = esc_base.to(dev)
     n_elems = sum(x.numel() for ent in slots for x in ent['x'])
-    tiles_per_launch = 2 * per * S4_HEADS * (half // BLOCK)
+    span_elems = per * S4_HEADS * half * S4_DIM
+    spans_per_launch = 2 if 4 * span_elems < 2 ** 31 else 1      # K and V of one span, or of both spans of the layer
+    tiles_per_launch = 2 * spans_per_launch * per * S4_HEADS * (half // BLOCK)
     # launches of neighbouring layers rotate over a few streams (each with its own pack scratch and unpack
     # destination): the tail of one launch and its compaction pass overlap the next launch
     n_lanes_cfg = max(1, min(int(args.lanes), 4))
@@ -427,14 +430,17 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
     def pack_layer(li: int, si: int = 0) -> None:
         ent = slots[li]
         ws, stream = ws2[si], lanes[si].cuda_stream
-        for si, span in enumerate(('a', 'b')):
-            pair = ent[span]
-            groups = [pair] if pair[0].nbits == pair[1].nbits else [[pair[0]], [pair[1]]]
-            for grp in groups:
+        # (tensor, histogram) of every job; tensors of one code length share a launch, both spans of the
+        # layer together where a launch of four tensors stays below 2**31 elements (N >= 2)
+        todo = [(s, hists[li, sp, wi].data_ptr()) for sp, span in enumerate(('a', 'b')) for wi, s in enumerate(ent[span])]
+        batches = [todo] if spans_per_launch == 2 else [todo[:2], todo[2:]]
+        for batch in batches:
+            for nb in sorted({s.nbits for s, _ in batch}):
+                grp = [(s, h) for s, h in batch if s.nbits == nb]
                 jobs = (_lib.PackJob * len(grp))()
-                for jb, s in zip(jobs, grp):
-                    fill_pack_job(jb, s, hists[li, si, pair.index(s)].data_ptr())
-                rc = L.adacode_pack_jobs(ctypes.addressof(jobs), len(grp), per, S4_HEADS, BLOCK, S4_DIM, grp[0].nbits,
+                for jb, (s, h) in zip(jobs, grp):
+                    fill_pack_job(jb, s, h)
+                rc = L.adacode_pack_jobs(ctypes.addressof(jobs), len(grp), per, S4_HEADS, BLOCK, S4_DIM, nb,
                                          ws.data_ptr(), ws.numel(), status.data_ptr(), stream)
                 if rc:
                     _lib.check(rc, 'adacode_pack_jobs')
@@ -675,7 +681,8 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
                      'traffic': round(PACK_DRAM_BYTES_PER_ELEM * n_elems / pack_calls),
                      'algorithmic_bytes_per_launch': round(alg / pack_calls),
                      'avg_launch_us': round(pack_ms * 1e3 / pack_calls, 2),
-                     'launch': 'one adacode_pack_jobs call: K and V of one 4096-token span'},
+                     'launch': 'one adacode_pack_jobs call: K and V of ' +
+                               ('one 4096-token span' if spans_per_launch == 1 else 'both 4096-token spans of a layer')},
         'roofline_unpack': {'bound': 'hbm', 'kernel': 'k_unpack_pipe', 'achieved': round(ach_unpack, 1),
                             'peak': peak, 'unit': 'GB/s', 'frac': round(ach_unpack / peak, 4),
                             'avg_launch_us': round(unpack_ms * 1e3 / unpack_launches, 2),
