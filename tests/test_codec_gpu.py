@@ -267,13 +267,15 @@ def test_randomised_shapes_windows_and_escape_rates(cuda_device):
     codec.check_device_status(cuda_device)
 
 
-def test_pack_jobs_three_tensors_one_launch(cuda_device):
+@pytest.mark.parametrize('D', [128, 64])
+def test_pack_jobs_three_tensors_one_launch(cuda_device, D):
     """``adacode_pack_jobs`` through the raw C ABI: three tensors of one shape family (different
-    block counts, windows, one without a histogram) in one launch equal three ordinary packs."""
+    block counts, windows, one without a histogram) in one launch equal three ordinary packs
+    (head_dim 64: tiles of 8192 elements, which the pack kernel runs on its 8-warp geometry)."""
     import ctypes
     from adacode_b200 import _lib, codec
     L = _lib.lib()
-    B, H, D, nbits = 2, 3, 128, 3
+    B, H, nbits = 2, 3, 3
     specs = [(384, 129, True), (128, 127, False), (256, 131, True)]
     xs = [synth.inject_escapes(synth.kv_tensor((B, H, S, D), seed=70 + i, key_offset=bool(i & 1)), seed=80 + i,
                                left=r - 7, right=r).to(cuda_device) for i, (S, r, _) in enumerate(specs)]
@@ -322,7 +324,7 @@ def test_pack_jobs_three_tensors_one_launch(cuda_device):
                                ws.numel(), status.data_ptr(), 0) == _lib.ERR_INVALID_ARG
 
 
-@pytest.mark.parametrize('D', [128, 96, 512])
+@pytest.mark.parametrize('D', [128, 96, 512, 64, 1040])
 def test_unpack_jobs_and_token_major_destination(cuda_device, D):
     """Keys and values unpacked by one launch (``adacode_unpack_jobs``), the keys into a
     destination whose token rows are not adjacent ([B, S, H, D] memory viewed as [B, H, S, D])."""
