@@ -603,10 +603,18 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
 // pack
 // ---------------------------------------------------------------------------------------
 
-// In-window histogram over several group words at once.  The match bit of a code lands on the
-// least significant bit of its N-bit slot, so N groups (4 for N <= 2) can be overlaid on one
-// 32-bit word before the population count: one lop3 + popc + add per code value for up to
-// 32 elements.
+// In-window histogram over several group words at once.  Bit i of a code lands on the least
+// significant bit of its N-bit slot, so N groups (4 for N <= 2) can be overlaid on one 32-bit
+// word: plane[i] then holds bit i of up to 32 codes.
+//
+// What is counted is not "how many codes equal v" (one three-input AND with complements, a mask
+// and a population count per value) but, for every non-empty proper subset m of the N code bits,
+// "how many codes have all bits of m set" (f(m): one AND of the planes named by m, no AND at all
+// for single bits).  Together with the number of elements f(0) and the number of escapes x(0),
+// which the kernel knows anyway, the per-value counts follow at flush time by inverting the
+// superset sums: f(full) = (-1)^N (x(0) - sum_{m != full} (-1)^|m| f(m)), then
+// x(c) = sum_{m >= c} (-1)^(|m|-|c|) f(m).  For N = 3 that is 6 population counts and 3 ANDs per
+// 24 elements instead of 7 and 14; for N = 1 nothing at all.
 template <int N>
 struct GroupsPerWord { static constexpr int v = (N == 3) ? 3 : 4; };
 
@@ -617,40 +625,45 @@ __device__ __forceinline__ uint32_t overlay_shift(int j) {
     return (uint32_t)(8 * j);                                 // N == 1: one byte per group
 }
 
-// Counters live in registers, two 16-bit fields per register: a thread sees fewer than 2**31 /
-// (CTAs x threads) elements in one launch, far below 65536 per code value.
+// Counters live in registers, two 16-bit fields per register: field 0 counts elements, field m
+// (0 < m < 2^N - 1) the codes with all bits of m set, field 2^N - 1 the escapes.  A thread adds at
+// most 32 to a field per unit, so the fields are flushed every 1024 units at the latest.
 template <int N>
 struct HistRegs { static constexpr int v = (1 << N) / 2 > 0 ? (1 << N) / 2 : 1; };
+
+template <int N>
+__device__ __forceinline__ void bump_field(uint32_t (&cnt2)[HistRegs<N>::v], int field, uint32_t by) {
+    cnt2[field >> 1] = by * ((field & 1) ? 65536u : 1u) + cnt2[field >> 1];
+}
 
 template <int N, int NG>
 __device__ __forceinline__ void count_codes_overlaid(const uint32_t (&g)[NG], uint32_t (&cnt2)[HistRegs<N>::v]) {
     constexpr int GPW = GroupsPerWord<N>::v;
+    constexpr int FULL = (1 << N) - 1;
     constexpr uint32_t M = SlotLsb<N>::v;
 #pragma unroll
     for (int base = 0; base < NG; base += GPW) {
         uint32_t plane[N];
-        uint32_t used = 0;
 #pragma unroll
         for (int i = 0; i < N; ++i) plane[i] = 0;
 #pragma unroll
         for (int j = 0; j < GPW; ++j) {
             if (base + j < NG) {
                 const uint32_t sh = overlay_shift<N>(j);
-                used |= M << sh;
 #pragma unroll
                 for (int i = 0; i < N; ++i) plane[i] = ((g[base + j] >> i) & M) * (1u << sh) + plane[i];
             }
         }
 #pragma unroll
-        for (int v = 1; v < (1 << N); ++v) {
-            uint32_t m = used;
+        for (int m = 1; m < FULL; ++m) {
+            uint32_t all = 0xFFFFFFFFu;
 #pragma unroll
-            for (int i = 0; i < N; ++i) m &= ((v >> i) & 1) ? plane[i] : ~plane[i];
-            cnt2[v >> 1] = (uint32_t)__popc(m) * ((v & 1) ? 65536u : 1u) + cnt2[v >> 1];
+            for (int i = 0; i < N; ++i)
+                if ((m >> i) & 1) all &= plane[i];
+            bump_field<N>(cnt2, m, (uint32_t)__popc(all));
         }
     }
 }
-
 
 struct PackUnitMeta {
     uint8_t *sm_dst;       // sign/mantissa bytes of the unit
@@ -789,16 +802,31 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
     if (tid == 0) *pa.done = 0u;
 }
 
-// Per-thread in-window counters (16-bit fields) -> the CTA's shared histogram.
+// Per-thread counter fields -> the CTA's shared histogram: the fields are summed over the warp, the
+// superset sums inverted (see count_codes_overlaid) and the per-value counts added by lane 0.
 template <int N>
 __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::v], int left, int *s_hist) {
+    constexpr int FULL = (1 << N) - 1;
     const int lane = threadIdx.x & 31;
+    int f[1 << N];
 #pragma unroll
-    for (int v = 1; v < (1 << N); ++v) {
-        const uint32_t mine = (cnt2[v >> 1] >> (16 * (v & 1))) & 0xFFFFu;
-        const uint32_t sum = __reduce_add_sync(kFull, mine);
+    for (int m = 0; m <= FULL; ++m)
+        f[m] = (int)__reduce_add_sync(kFull, (cnt2[m >> 1] >> (16 * (m & 1))) & 0xFFFFu);
+    // f[FULL] holds the escapes x(0); f(full) follows from x(0) = sum_m (-1)^|m| f(m)
+    int alt = 0;
+#pragma unroll
+    for (int m = 0; m < FULL; ++m) alt += (__builtin_popcount(m) & 1) ? -f[m] : f[m];
+    f[FULL] = (N & 1) ? alt - f[FULL] : f[FULL] - alt;
+    // inverse of the superset sums, one code bit at a time
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+#pragma unroll
+        for (int m = 0; m <= FULL; ++m)
+            if (!((m >> i) & 1)) f[m] -= f[m | (1 << i)];
+#pragma unroll
+    for (int v = 1; v <= FULL; ++v) {
         const int bin = left + v;
-        if (lane == 0 && sum != 0 && bin >= 0 && bin < 256) atomicAdd(&s_hist[bin], (int)sum);
+        if (lane == 0 && f[v] != 0 && bin >= 0 && bin < 256) atomicAdd(&s_hist[bin], f[v]);
     }
 #pragma unroll
     for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
@@ -850,7 +878,13 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
         zc[k] = __popc(zm[k][0]) + __popc(zm[k][1]);
         smv[k] = make_uint4(smw[0], smw[1], smw[2], smw[3]);
     }
-    if (HIST) count_codes_overlaid<N, kPCPT * 2>(g, cnt2);
+    if (HIST) {
+        count_codes_overlaid<N, kPCPT * 2>(g, cnt2);
+        const int first = warp * (kPCPT * 32) + lane;
+        const int mine = (first < chunks ? 16 : 0) + (first + 32 < chunks ? 16 : 0);  // elements this thread encoded
+        bump_field<N>(cnt2, 0, (uint32_t)mine);
+        bump_field<N>(cnt2, (1 << N) - 1, (uint32_t)(zc[0] + zc[1]));
+    }
 
     int incl[kPCPT];
     const int wtot = warp_scan_counts(zc, incl);
