@@ -74,8 +74,8 @@ def workload_config(world: int) -> dict:
         'sequences_per_gpu': S4_BATCH // world, 'block_size': BLOCK,
         'l2': 'per-rank working set of a step (inputs + planes) exceeds L2 many times over; all layers are packed '
               'before any is unpacked, so nothing is re-read from L2',
-        'launches': 'K and V of a span share one launch (adacode_pack_jobs / adacode_unpack_jobs; both spans of a layer '
-                    'where four tensors stay below 2**31 elements, i.e. from two GPUs up); launches of '
+        'launches': 'K and V of both spans of a layer share one pack launch (adacode_pack_jobs, four tensors, 2**30 '
+                    'elements at N = 1) and K and V of a layer one unpack launch (adacode_unpack_jobs); launches of '
                     'neighbouring layers rotate over three streams',
     }
 
@@ -431,7 +431,7 @@ def stress_workload(args, dev, world: int, rank: int, local_rank: int) -> dict:
         ent = slots[li]
         ws, stream = ws2[si], lanes[si].cuda_stream
         # (tensor, histogram) of every job; tensors of one code length share a launch, both spans of the
-        # layer together where a launch of four tensors stays below 2**31 elements (N >= 2)
+        # layer together as long as a launch of four tensors stays below 2**31 elements
         todo = [(s, hists[li, sp, wi].data_ptr()) for sp, span in enumerate(('a', 'b')) for wi, s in enumerate(ent[span])]
         batches = [todo] if spans_per_launch == 2 else [todo[:2], todo[2:]]
         for batch in batches:
