@@ -405,11 +405,15 @@ template <int N, class G>
 __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStageT<G> &st, uint64_t *empty_bar,
                                             int &consumed, int D, int32_t *status) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const UnitMeta m = st.meta;
-    const long long ds = m.ds;
+    // only what the common path needs is read from the unit's description now; the fields of the
+    // rare global-memory escape path are read where that path is taken (before the stage is released)
+    const UnitMeta &meta = st.meta;
+    const int elems = meta.elems, esc_staged = meta.esc_staged, esc_shift = meta.esc_shift;
+    uint16_t *const dst = meta.dst;
+    const long long ds = meta.ds;
     const bool rows_contig = (ds == D);
-    if (m.first_unit_of_tile) consumed = 0;
-    const int chunks = m.elems >> 4;
+    if (meta.first_unit_of_tile) consumed = 0;
+    const int chunks = elems >> 4;
 
     uint4 o[kPCPT][2];
     uint32_t zm[kPCPT][2];
@@ -436,7 +440,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
     if (zc[0] + zc[1] != 0) {
         // ranks inside the tile of the first escape of either chunk
         const int r0 = consumed + wprefix + incl[0] - zc[0], r1 = consumed + wprefix + incl[1] - zc[1];
-        const bool staged = (zc[0] == 0 || r0 + zc[0] <= m.esc_staged) && (zc[1] == 0 || r1 + zc[1] <= m.esc_staged);
+        const bool staged = (zc[0] == 0 || r0 + zc[0] <= esc_staged) && (zc[1] == 0 || r1 + zc[1] <= esc_staged);
         if (staged) {
             // One loop over the escapes of both chunks (four groups): a warp iterates as often as its
             // busiest lane has escapes, and per-lane totals over 32 elements vary much less than
@@ -446,7 +450,7 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
                             (compress_slots<N>(zm[1][0]) << 8) | compress_slots<N>(zm[1][1]);
             // The exponent field in s.out is zero at escaped positions (code 0 decodes to 0), so the
             // escape byte is OR-ed in with a shared-memory reduction: no read-modify-write round trip.
-            const uint8_t *ep = st.esc + m.esc_shift + r0;
+            const uint8_t *ep = st.esc + esc_shift + r0;
             const int skip = r1 - r0 - zc[0];             // from chunk 0's escapes to chunk 1's
             uint32_t *ow32 = reinterpret_cast<uint32_t *>(s.out + c0 * 16);
             int n = 0;
@@ -460,6 +464,8 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
             }
         } else {
             // beyond the staged window (or beyond the stream): fetch from global memory
+            const uint8_t *g_esc = meta.esc;
+            const long long g_len = meta.esc_len, g_start = meta.esc_tile_start;
 #pragma unroll 1
             for (int k = 0; k < kPCPT; ++k) {
                 uint16_t *ow = s.out + (c0 + k * 32) * 16;
@@ -471,8 +477,8 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
                         const int pos = 31 - __clz(z);
                         z ^= 1u << pos;
                         uint32_t e = 0;
-                        if (r < m.esc_staged) e = st.esc[m.esc_shift + r];
-                        else if (m.esc_tile_start + r < m.esc_len) e = m.esc[m.esc_tile_start + r];
+                        if (r < esc_staged) e = st.esc[esc_shift + r];
+                        else if (g_start + r < g_len) e = g_esc[g_start + r];
                         else atomicOr(status, ADACODE_STATUS_ESCAPE_UNDERRUN);
                         ++r;
                         uint16_t *pw = ow + (q * 8 + 7 - pos / N);
@@ -487,13 +493,13 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
     fence_async_smem();
     consumer_sync<G::kConsumers>();
     if (rows_contig) {
-        if (tid == 0 && m.elems > 0) {
-            bulk_store(m.dst, s.out, (uint32_t)m.elems * 2u);
+        if (tid == 0 && elems > 0) {
+            bulk_store(dst, s.out, (uint32_t)elems * 2u);
             bulk_commit();
         }
     } else {
-        const int rows = m.elems / D;
-        for (int r = tid; r < rows; r += G::kConsumers) bulk_store(m.dst + (long long)r * ds, s.out + r * D, (uint32_t)D * 2u);
+        const int rows = elems / D;
+        for (int r = tid; r < rows; r += G::kConsumers) bulk_store(dst + (long long)r * ds, s.out + r * D, (uint32_t)D * 2u);
         bulk_commit();
     }
 }
