@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
                 const EscWindow w = esc_window(t);
                 const int stg = it % kStages;
                 mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a.status);
-                issue_unit(s.stage[stg], &s.full[stg], t, w, 0, kTileTokens, kAD, nullptr, true, a.status);
+                issue_unit(s.stage[stg], s.stage[stg].meta, &s.full[stg], t, w, 0, kTileTokens, kAD, nullptr, true, a.status);
             }
         }
         return;

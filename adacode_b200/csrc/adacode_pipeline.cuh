@@ -68,19 +68,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait; on expiry flags the status word and returns anyway.
-// Once any wait of the launch has timed out, the others stop waiting as well (they look at the
-// status word now and then), so that a broken launch ends in about the time of one expired wait.
+// Bounded wait; on expiry flags the status word and returns anyway (false: the barrier did not
+// complete).  Once any wait of the launch has timed out, the others stop waiting as well (they look
+// at the status word now and then), so that a broken launch ends in about the time of one expired
+// wait.  A consumer whose wait failed keeps computing (it must reach every barrier) but stores
+// nothing to global memory any more: it may be looking at a half-written unit description.
 __device__ __forceinline__ bool launch_timed_out(const int32_t *status) {
     return (*reinterpret_cast<const volatile int32_t *>(status) & ADACODE_STATUS_TIMEOUT) != 0;
 }
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status,
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status,
                                           uint32_t limit = kMaxPolls) {
     for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return;
-        if ((i & 4095u) == 4095u && launch_timed_out(status)) return;
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 4095u) == 4095u && launch_timed_out(status)) return false;
     }
     atomicOr(status, ADACODE_STATUS_TIMEOUT);
+    return false;
 }
 // global -> shared bulk copy, completion counted in bytes on `bar`; 16-byte aligned, size % 16 == 0
 __device__ __forceinline__ void bulk_load(void *sdst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
@@ -197,6 +200,12 @@ struct alignas(128) UnpackSmemT {
     UnpackStageT<G> stage[kStages];
     alignas(128) uint16_t out[G::kUnit];
     alignas(16) uint32_t lut[1024];   // decode table of the current (left, nbits)
+    // Unit descriptions live in a ring of their own, twice as deep as the stages: a consumer reads
+    // the destination of unit i after it has released stage i % kStages, and the producer writes
+    // the description of unit i + 2 * kStages only after every consumer has released unit
+    // i + kStages, i.e. after it is done with unit i altogether.  So nobody has to keep a
+    // description in registers through a unit.
+    alignas(16) UnitMeta meta_ring[2 * kStages];
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
     int warp_tot[G::kWarps];
@@ -321,11 +330,11 @@ __device__ __forceinline__ EscWindow esc_window(const TileSrc &t) {
 }
 
 // Producer warp, stage known to be free: describe the unit (rows [row0, row0 + rows) of tile t) in
-// the stage's meta block and start its bulk copies against `full_bar`.
+// `m` and start its bulk copies against `full_bar`.
 template <class Stage>
-__device__ __forceinline__ void issue_unit(Stage &st, uint64_t *full_bar, const TileSrc &t, const EscWindow &w,
-                                           int row0, int rows, int D, uint16_t *dst, bool first_unit,
-                                           int32_t *status, bool withhold = false) {
+__device__ __forceinline__ void issue_unit(Stage &st, UnitMeta &m, uint64_t *full_bar, const TileSrc &t,
+                                           const EscWindow &w, int row0, int rows, int D, uint16_t *dst,
+                                           bool first_unit, int32_t *status, bool withhold = false) {
     const int lane = threadIdx.x & 31;
     if (w.tail > 0) {
         if (lane < w.tail) st.esc[w.win + lane] = w.a0[w.win + lane];
@@ -335,7 +344,6 @@ __device__ __forceinline__ void issue_unit(Stage &st, uint64_t *full_bar, const 
         const int elems = rows * D;
         const uint8_t *src_sm = t.sm + (long long)row0 * D;
         const uint8_t *src_cd = t.codes + (long long)row0 * D * t.nbits / 8;
-        UnitMeta &m = st.meta;
         m.dst = dst;
         m.esc = t.esc, m.esc_len = t.esc_len, m.esc_tile_start = t.esc_start;
         m.esc_staged = w.staged, m.esc_shift = w.shift;
@@ -402,18 +410,14 @@ __device__ __forceinline__ void decode_chunks(const Stage &st, const uint32_t *l
 }
 
 template <int N, class G>
-__device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStageT<G> &st, uint64_t *empty_bar,
-                                            int &consumed, int D, int32_t *status) {
+__device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStageT<G> &st, const UnitMeta &meta,
+                                            uint64_t *empty_bar, int &consumed, int D, int32_t *status, bool broken) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // only what the common path needs is read from the unit's description now; the fields of the
-    // rare global-memory escape path are read where that path is taken (before the stage is released)
-    const UnitMeta &meta = st.meta;
-    const int elems = meta.elems, esc_staged = meta.esc_staged, esc_shift = meta.esc_shift;
-    uint16_t *const dst = meta.dst;
-    const long long ds = meta.ds;
-    const bool rows_contig = (ds == D);
+    // only what the common path needs is read from the unit's description up front; the fields of
+    // the rare global-memory escape path and the destination are read where they are used
+    const int esc_staged = meta.esc_staged, esc_shift = meta.esc_shift;
     if (meta.first_unit_of_tile) consumed = 0;
-    const int chunks = elems >> 4;
+    const int chunks = meta.elems >> 4;
 
     uint4 o[kPCPT][2];
     uint32_t zm[kPCPT][2];
@@ -472,7 +476,8 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
                 int r = k == 0 ? r0 : r1;
 #pragma unroll 1
                 for (int q = 0; q < 2; ++q) {
-                    uint32_t z = zm[k][q];
+                    // (selects, not zm[k][q]: a run-time index would move the array to local memory)
+                    uint32_t z = k == 0 ? (q == 0 ? zm[0][0] : zm[0][1]) : (q == 0 ? zm[1][0] : zm[1][1]);
                     while (z) {
                         const int pos = 31 - __clz(z);
                         z ^= 1u << pos;
@@ -492,13 +497,17 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
     mbar_arrive(empty_bar);    // this thread no longer reads the stage
     fence_async_smem();
     consumer_sync<G::kConsumers>();
-    if (rows_contig) {
-        if (tid == 0 && elems > 0) {
-            bulk_store(dst, s.out, (uint32_t)elems * 2u);
+    const long long ds = meta.ds;
+    if (broken) {
+        // (nothing is stored)
+    } else if (ds == D) {
+        if (tid == 0 && meta.elems > 0) {
+            bulk_store(meta.dst, s.out, (uint32_t)meta.elems * 2u);
             bulk_commit();
         }
     } else {
-        const int rows = elems / D;
+        const int rows = meta.elems / D;
+        uint16_t *const dst = meta.dst;
         for (int r = tid; r < rows; r += G::kConsumers) bulk_store(dst + (long long)r * ds, s.out + r * D, (uint32_t)D * 2u);
         bulk_commit();
     }
@@ -529,6 +538,12 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
             mbar_init(&s.empty[i], G::kConsumers);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < 2 * kStages) {
+        // an empty unit: what a consumer sees if it gives up waiting before the first description is written
+        UnitMeta &m = s.meta_ring[tid];
+        m.dst = nullptr, m.esc = nullptr, m.esc_len = 0, m.esc_tile_start = 0, m.esc_staged = 0, m.esc_shift = 0;
+        m.elems = 0, m.left = 0, m.nbits = 1, m.first_unit_of_tile = 1, m.ds = 0;
     }
     __syncthreads();
 
@@ -561,7 +576,8 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
                     mbar_wait(&s.empty[stg], ((it / kStages) & 1) ^ 1, a0.status, ja.poll_limit);
                     const int row0 = u * unit_rows;
                     const int rows = min(unit_rows, a0.seq_tile - row0);
-                    issue_unit(s.stage[stg], &s.full[stg], t, w, row0, rows, a0.D, t.dst + (long long)row0 * t.ds,
+                    issue_unit(s.stage[stg], s.meta_ring[it % (2 * kStages)], &s.full[stg], t, w, row0, rows, a0.D,
+                               t.dst + (long long)row0 * t.ds,
                                u == 0, a0.status, blockIdx.x == 0 && (int)it == ja.withhold_unit);
                 }
             }
@@ -576,29 +592,34 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
     }
 
     // ---------------- consumer warps ----------------
-    uint32_t it = 0;
     int consumed = 0;
+    bool broken = false;                  // a wait of this warp ran out: compute on, store nothing
     int lut_left = 0, lut_nbits = 0;      // what s.lut currently encodes (nbits 0: nothing yet)
-    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        for (int u = 0; u < units_per_tile; ++u, ++it) {
-            const int stg = it % kStages;
-            if ((tid & 31) == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, a0.status, ja.poll_limit);
-            __syncwarp();
-            const UnpackStageT<G> &st = s.stage[stg];
-            const int nb = st.meta.nbits, lf = st.meta.left;
-            if (nb != lut_nbits || lf != lut_left) {
-                // uniform over the CTA: every consumer read the same meta.  The previous unit ended
-                // with a consumer barrier, so nobody still reads the old table.
-                build_decode_lut(s.lut, nb, lf, G::kConsumers);
-                lut_nbits = nb, lut_left = lf;
-                consumer_sync<G::kConsumers>();
-            }
-            switch (nb) {
-                case 1: unpack_unit<1>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
-                case 2: unpack_unit<2>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
-                case 3: unpack_unit<3>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
-                default: unpack_unit<4>(s, st, &s.empty[stg], consumed, a0.D, a0.status); break;
-            }
+    // (the consumers only count units: which tile a unit belongs to is in its description)
+    const uint32_t my_units =
+        n_tiles > (long long)blockIdx.x
+            ? (uint32_t)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * (uint32_t)units_per_tile
+            : 0u;
+    for (uint32_t it = 0; it < my_units; ++it) {
+        const int stg = it % kStages;
+        bool loaded = true;
+        if ((tid & 31) == 0) loaded = mbar_wait(&s.full[stg], (it / kStages) & 1, a0.status, ja.poll_limit);
+        broken |= !__shfl_sync(kFull, loaded, 0);
+        const UnpackStageT<G> &st = s.stage[stg];
+        const UnitMeta &meta = s.meta_ring[it % (2 * kStages)];
+        const int nb = meta.nbits, lf = meta.left;
+        if (nb != lut_nbits || lf != lut_left) {
+            // uniform over the CTA: every consumer read the same meta.  The previous unit ended
+            // with a consumer barrier, so nobody still reads the old table.
+            build_decode_lut(s.lut, nb, lf, G::kConsumers);
+            lut_nbits = nb, lut_left = lf;
+            consumer_sync<G::kConsumers>();
+        }
+        switch (nb) {
+            case 1: unpack_unit<1>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
+            case 2: unpack_unit<2>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
+            case 3: unpack_unit<3>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
+            default: unpack_unit<4>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
         }
     }
     bulk_wait_all();
@@ -686,7 +707,6 @@ struct PackUnitMeta {
 template <class G>
 struct alignas(128) PackStageT {
     alignas(128) uint16_t in[G::kUnit];
-    alignas(16) PackUnitMeta meta;
 };
 
 template <class G>
@@ -696,6 +716,7 @@ struct alignas(128) PackSmemT {
     alignas(128) uint8_t codes[G::kUnit / 2];
     alignas(128) uint8_t esc[G::kUnit];      // worst case: every element of a unit escapes
     alignas(16) uint8_t lut[256];      // exponent -> code (0 = outside the window)
+    alignas(16) PackUnitMeta meta_ring[2 * kStages];   // unit descriptions (see UnpackSmemT::meta_ring)
     alignas(8) uint64_t full[kStages];
     alignas(8) uint64_t empty[kStages];
     int warp_tot[G::kWarps];
@@ -839,11 +860,12 @@ __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::
 }
 
 template <int N, bool HIST, class G>
-__device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &st, uint64_t *empty_bar,
-                                          int &running, uint32_t (&cnt2)[HistRegs<N>::v]) {
+__device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &st, const PackUnitMeta &m,
+                                          uint64_t *empty_bar, int &running, uint32_t (&cnt2)[HistRegs<N>::v],
+                                          bool broken) {
     constexpr int CB = 2 * N;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const PackUnitMeta m = st.meta;
+    // (m lives in the description ring: its destination fields are read where the unit is stored)
     if (m.first_unit_of_tile) running = 0;
     const int chunks = m.elems >> 4;
 
@@ -932,7 +954,7 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
     fence_async_smem();
     consumer_sync<G::kConsumers>();
     running += unit_tot;
-    if (tid == 0) {
+    if (tid == 0 && !broken) {
         if (m.elems > 0) {
             bulk_store(m.sm_dst, s.sm, (uint32_t)m.elems);
             bulk_store(m.code_dst, s.codes, (uint32_t)m.elems * N / 8);
@@ -959,6 +981,12 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (HIST && tid < 256) s.hist[tid] = 0;
+    if (tid < 2 * kStages) {
+        // an empty unit: what a consumer sees if it gives up waiting before the first description is written
+        PackUnitMeta &m = s.meta_ring[tid];
+        m.sm_dst = m.code_dst = m.esc_dst = nullptr, m.unit_count = m.tile_count = nullptr;
+        m.elems = 0, m.first_unit_of_tile = 1, m.last_unit_of_tile = 0, m.job = 0;
+    }
     __syncthreads();
 
     const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
@@ -984,7 +1012,7 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
                 const int rows = min(unit_rows, pa.seq_tile - row0);
                 const int elems = rows * pa.D;
                 if (lane == 0) {
-                    PackUnitMeta &m = st.meta;
+                    PackUnitMeta &m = s.meta_ring[it % (2 * kStages)];
                     const int64_t e0 = lt * pa.tile_elems + (int64_t)row0 * pa.D;
                     m.sm_dst = jb.sign_mant + e0;
                     m.code_dst = jb.codes + e0 * N / 8;
@@ -1019,38 +1047,43 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
     uint32_t cnt2[HistRegs<N>::v];
 #pragma unroll
     for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
-    uint32_t it = 0;
     int running = 0;
+    bool broken = false;                  // a wait of this warp ran out: compute on, store nothing
     int cur_job = -1, cur_left = 0;
-    for (int64_t tile = blockIdx.x; tile < pa.n_tiles; tile += gridDim.x) {
-        for (int u = 0; u < upt; ++u, ++it) {
-            const int stg = it % kStages;
-            if (lane == 0) mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status, pa.poll_limit);
-            __syncwarp();
-            const int job = s.stage[stg].meta.job;
-            if (job != cur_job) {
-                // Uniform over the CTA (every consumer reads the same sequence of units): hand the finished
-                // job's histogram over and build the new job's code table.  The previous unit ended with
-                // a consumer barrier, so nobody still encodes with the old table.
-                if (HIST && cur_job >= 0) flush_code_counts<N>(cnt2, cur_left, s.hist);
-                consumer_sync<G::kConsumers>();
-                if (HIST && cur_job >= 0 && tid < 256) {
-                    const int hv = s.hist[tid];
-                    if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
-                    s.hist[tid] = 0;
-                }
-                cur_job = job;
-                cur_left = pa.job[job].left;
-                if (tid < 256) {
-                    const uint32_t code = (uint32_t)tid - (uint32_t)cur_left;
-                    s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
-                }
-                consumer_sync<G::kConsumers>();
+    // (the consumers only count units: which tile a unit belongs to is in its description)
+    const uint32_t my_units =
+        pa.n_tiles > (int64_t)blockIdx.x
+            ? (uint32_t)((pa.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * (uint32_t)upt
+            : 0u;
+    for (uint32_t it = 0; it < my_units; ++it) {
+        const int stg = it % kStages;
+        bool loaded = true;
+        if (lane == 0) loaded = mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status, pa.poll_limit);
+        broken |= !__shfl_sync(kFull, loaded, 0);
+        const PackUnitMeta &meta = s.meta_ring[it % (2 * kStages)];
+        const int job = meta.job;
+        if (job != cur_job) {
+            // Uniform over the CTA (every consumer reads the same sequence of units): hand the finished
+            // job's histogram over and build the new job's code table.  The previous unit ended with
+            // a consumer barrier, so nobody still encodes with the old table.
+            if (HIST && cur_job >= 0) flush_code_counts<N>(cnt2, cur_left, s.hist);
+            consumer_sync<G::kConsumers>();
+            if (HIST && cur_job >= 0 && tid < 256) {
+                const int hv = s.hist[tid];
+                if (hv != 0 && pa.job[cur_job].hist) atomicAdd(pa.job[cur_job].hist + tid, hv);
+                s.hist[tid] = 0;
             }
-            pack_unit<N, HIST, G>(s, s.stage[stg], &s.empty[stg], running, cnt2);
-            // the per-thread counters are 16-bit fields and grow by at most 32 per unit
-            if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
+            cur_job = job;
+            cur_left = pa.job[job].left;
+            if (tid < 256) {
+                const uint32_t code = (uint32_t)tid - (uint32_t)cur_left;
+                s.lut[tid] = (uint8_t)(code > ((1u << N) - 1u) ? 0u : code);
+            }
+            consumer_sync<G::kConsumers>();
         }
+        pack_unit<N, HIST, G>(s, s.stage[stg], meta, &s.empty[stg], running, cnt2, broken);
+        // the per-thread counters are 16-bit fields and grow by at most 32 per unit
+        if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
     }
     if (HIST && cur_job >= 0) {
         flush_code_counts<N>(cnt2, cur_left, s.hist);
