@@ -7,8 +7,10 @@
 // whole token rows of one tile, at most W x 1024 elements.  Two geometries are built: the wide one
 // (16 warps, units of a whole 128 x 128 tile, 2 CTAs per SM) for the pack kernel and the fused
 // attention kernel, the narrow one (8 warps, units of 8192 elements, 4 CTAs per SM) for the unpack
-// kernel, which measured 5-8 % faster with four smaller pipelines per SM than with two large ones
-// (the pack kernel measured 7 % slower that way: twice the escape slots and unit counts to compact).
+// kernel, which measured 5-8 % faster with four smaller pipelines per SM than with two large ones.
+// The pack kernel measured 7 % slower that way (twice the escape slots and unit counts to
+// compact) and takes the narrow geometry only for tiles of at most 8192 elements, which would
+// leave half the threads of a wide unit idle.
 //   producer warp : waits for a free stage, issues the unit's bulk loads (sign/mantissa and
 //                   code planes, or source rows) against the stage's "full" mbarrier, and
 //                   stages the tile's escape bytes with plain loads
