@@ -515,6 +515,29 @@ __device__ __forceinline__ void unpack_unit(UnpackSmemT<G> &s, const UnpackStage
     }
 }
 
+// Consumer warp: wait (bounded) until unit `it` is loaded; false if the wait gave up.
+template <class G>
+__device__ __forceinline__ bool wait_loaded(UnpackSmemT<G> &s, uint32_t it, int32_t *status, uint32_t poll_limit) {
+    bool loaded = true;
+    if ((threadIdx.x & 31) == 0) loaded = mbar_wait(&s.full[it % kStages], (it / kStages) & 1, status, poll_limit);
+    return __shfl_sync(kFull, loaded, 0);
+}
+
+// Units it, it + 1, ... as long as they carry code length N and window `left` (the decode table
+// in s.lut); returns the first unit that does not, already waited for, or n_units.
+template <int N, class G>
+__device__ __forceinline__ uint32_t unpack_run(UnpackSmemT<G> &s, uint32_t it, uint32_t n_units, int left, int &consumed,
+                                               bool &broken, int D, int32_t *status, uint32_t poll_limit) {
+    for (;;) {
+        const int stg = it % kStages;
+        unpack_unit<N>(s, s.stage[stg], s.meta_ring[it % (2 * kStages)], &s.empty[stg], consumed, D, status, broken);
+        if (++it >= n_units) return it;
+        broken |= !wait_loaded(s, it, status, poll_limit);
+        const UnitMeta &next = s.meta_ring[it % (2 * kStages)];
+        if (next.nbits != N || next.left != left) return it;
+    }
+}
+
 constexpr int kMaxJobs = 8;
 
 // Up to kMaxJobs destinations in one launch; job j owns the tiles [tile0[j], tile0[j + 1]).
@@ -602,26 +625,26 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
         n_tiles > (long long)blockIdx.x
             ? (uint32_t)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * (uint32_t)units_per_tile
             : 0u;
-    for (uint32_t it = 0; it < my_units; ++it) {
-        const int stg = it % kStages;
-        bool loaded = true;
-        if ((tid & 31) == 0) loaded = mbar_wait(&s.full[stg], (it / kStages) & 1, a0.status, ja.poll_limit);
-        broken |= !__shfl_sync(kFull, loaded, 0);
-        const UnpackStageT<G> &st = s.stage[stg];
+    // Units of one code length and window are handled by a loop of their own (unpack_run<N>), so
+    // that the compiler schedules each code length's loop body by itself; this outer loop only
+    // takes over when the table has to change.
+    uint32_t it = 0;
+    while (it < my_units) {
+        broken |= !wait_loaded(s, it, a0.status, ja.poll_limit);      // returns at once if unpack_run waited already
         const UnitMeta &meta = s.meta_ring[it % (2 * kStages)];
         const int nb = meta.nbits, lf = meta.left;
         if (nb != lut_nbits || lf != lut_left) {
-            // uniform over the CTA: every consumer read the same meta.  The previous unit ended
-            // with a consumer barrier, so nobody still reads the old table.
+            // uniform over the CTA: every consumer read the same description.  The previous unit
+            // ended with a consumer barrier, so nobody still reads the old table.
             build_decode_lut(s.lut, nb, lf, G::kConsumers);
             lut_nbits = nb, lut_left = lf;
             consumer_sync<G::kConsumers>();
         }
         switch (nb) {
-            case 1: unpack_unit<1>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
-            case 2: unpack_unit<2>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
-            case 3: unpack_unit<3>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
-            default: unpack_unit<4>(s, st, meta, &s.empty[stg], consumed, a0.D, a0.status, broken); break;
+            case 1: it = unpack_run<1>(s, it, my_units, lf, consumed, broken, a0.D, a0.status, ja.poll_limit); break;
+            case 2: it = unpack_run<2>(s, it, my_units, lf, consumed, broken, a0.D, a0.status, ja.poll_limit); break;
+            case 3: it = unpack_run<3>(s, it, my_units, lf, consumed, broken, a0.D, a0.status, ja.poll_limit); break;
+            default: it = unpack_run<4>(s, it, my_units, lf, consumed, broken, a0.D, a0.status, ja.poll_limit); break;
         }
     }
     bulk_wait_all();
