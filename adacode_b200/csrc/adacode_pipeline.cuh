@@ -1080,13 +1080,17 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
         pa.n_tiles > (int64_t)blockIdx.x
             ? (uint32_t)((pa.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * (uint32_t)upt
             : 0u;
-    for (uint32_t it = 0; it < my_units; ++it) {
-        const int stg = it % kStages;
+    // Units of one job run in an inner loop of their own; this outer loop only takes over when the
+    // job (and with it the window and the histogram) changes.
+    auto wait_loaded = [&](uint32_t u) {
         bool loaded = true;
-        if (lane == 0) loaded = mbar_wait(&s.full[stg], (it / kStages) & 1, pa.status, pa.poll_limit);
-        broken |= !__shfl_sync(kFull, loaded, 0);
-        const PackUnitMeta &meta = s.meta_ring[it % (2 * kStages)];
-        const int job = meta.job;
+        if (lane == 0) loaded = mbar_wait(&s.full[u % kStages], (u / kStages) & 1, pa.status, pa.poll_limit);
+        return (bool)__shfl_sync(kFull, loaded, 0);
+    };
+    uint32_t it = 0;
+    while (it < my_units) {
+        broken |= !wait_loaded(it);               // returns at once if the inner loop waited already
+        const int job = s.meta_ring[it % (2 * kStages)].job;
         if (job != cur_job) {
             // Uniform over the CTA (every consumer reads the same sequence of units): hand the finished
             // job's histogram over and build the new job's code table.  The previous unit ended with
@@ -1106,9 +1110,15 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
             }
             consumer_sync<G::kConsumers>();
         }
-        pack_unit<N, HIST, G>(s, s.stage[stg], meta, &s.empty[stg], running, cnt2, broken);
-        // the per-thread counters are 16-bit fields and grow by at most 32 per unit
-        if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
+        for (;;) {
+            const int stg = it % kStages;
+            pack_unit<N, HIST, G>(s, s.stage[stg], s.meta_ring[it % (2 * kStages)], &s.empty[stg], running, cnt2, broken);
+            // the per-thread counters are 16-bit fields and grow by at most 32 per unit
+            if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
+            if (++it >= my_units) break;
+            broken |= !wait_loaded(it);
+            if (s.meta_ring[it % (2 * kStages)].job != cur_job) break;
+        }
     }
     if (HIST && cur_job >= 0) {
         flush_code_counts<N>(cnt2, cur_left, s.hist);
