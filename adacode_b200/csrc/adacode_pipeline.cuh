@@ -884,7 +884,8 @@ __device__ __forceinline__ void flush_code_counts(uint32_t (&cnt2)[HistRegs<N>::
     for (int v = 0; v < HistRegs<N>::v; ++v) cnt2[v] = 0;
 }
 
-template <int N, bool HIST, class G>
+// FULL: the unit has G::kUnit elements (every thread has both of its chunks), so nothing is predicated.
+template <int N, bool HIST, class G, bool FULL>
 __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &st, const PackUnitMeta &m,
                                           uint64_t *empty_bar, int &running, uint32_t (&cnt2)[HistRegs<N>::v],
                                           bool broken) {
@@ -892,7 +893,7 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // (m lives in the description ring: its destination fields are read where the unit is stored)
     if (m.first_unit_of_tile) running = 0;
-    const int chunks = m.elems >> 4;
+    const int chunks = FULL ? G::kUnit / 16 : m.elems >> 4;
 
     uint4 smv[kPCPT];
     uint32_t g[kPCPT * 2], zm[kPCPT][2];
@@ -900,7 +901,7 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = warp * (kPCPT * 32) + k * 32 + lane;
-        const bool valid = c < chunks;
+        const bool valid = FULL || c < chunks;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
         if (valid) {
             const uint4 *p = reinterpret_cast<const uint4 *>(st.in + c * 16);
@@ -934,7 +935,7 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
     if (HIST) {
         count_codes_overlaid<N, kPCPT * 2>(g, cnt2);
         const int first = warp * (kPCPT * 32) + lane;
-        const int mine = (first < chunks ? 16 : 0) + (first + 32 < chunks ? 16 : 0);  // elements this thread encoded
+        const int mine = FULL ? 32 : (first < chunks ? 16 : 0) + (first + 32 < chunks ? 16 : 0);  // elements this thread encoded
         bump_field<N>(cnt2, 0, (uint32_t)mine);
         bump_field<N>(cnt2, (1 << N) - 1, (uint32_t)(zc[0] + zc[1]));
     }
@@ -951,7 +952,7 @@ __device__ __forceinline__ void pack_unit(PackSmemT<G> &s, const PackStageT<G> &
 #pragma unroll
     for (int k = 0; k < kPCPT; ++k) {
         const int c = c0 + k * 32;
-        if (c < chunks) {
+        if (FULL || c < chunks) {
             *reinterpret_cast<uint4 *>(s.sm + c * 16) = smv[k];
             const uint32_t gg[2] = {g[2 * k], g[2 * k + 1]};
             store_chunk_codes<N, 16>(s.codes + c * CB, gg);
@@ -1112,7 +1113,9 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
         }
         for (;;) {
             const int stg = it % kStages;
-            pack_unit<N, HIST, G>(s, s.stage[stg], s.meta_ring[it % (2 * kStages)], &s.empty[stg], running, cnt2, broken);
+            const PackUnitMeta &meta = s.meta_ring[it % (2 * kStages)];
+            if (meta.elems == G::kUnit) pack_unit<N, HIST, G, true>(s, s.stage[stg], meta, &s.empty[stg], running, cnt2, broken);
+            else pack_unit<N, HIST, G, false>(s, s.stage[stg], meta, &s.empty[stg], running, cnt2, broken);
             // the per-thread counters are 16-bit fields and grow by at most 32 per unit
             if (HIST && (it & 1023u) == 1023u) flush_code_counts<N>(cnt2, cur_left, s.hist);
             if (++it >= my_units) break;
