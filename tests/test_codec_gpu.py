@@ -388,3 +388,27 @@ def test_status_word_timeout_of_a_bounded_wait(cuda_device):
     codec.unpack_chunk(chunk, out)
     assert np.array_equal(_u16(out), _u16(x_cpu))
     codec.check_device_status(cuda_device)
+
+
+def test_code_counters_are_flushed_on_a_launch_of_very_many_small_tiles(cuda_device):
+    """The pack kernel counts codes in 16-bit register fields and empties them every 1024 units.
+    A CTA only gets that far with tiny tiles: 640 000 tiles of 128 x 16 elements in one launch give
+    each of the 592 CTAs more than 1024 units.  The histogram must equal a plain count."""
+    from adacode_b200 import codec
+    B, H, blocks, D = 8, 8, 10000, 16
+    gen = torch.Generator(device=cuda_device)
+    gen.manual_seed(5)
+    x = torch.empty((B, H, blocks * 128, D), dtype=torch.bfloat16, device=cuda_device)
+    for b in range(B):
+        x[b] = (torch.randn((H, blocks * 128, D), generator=gen, device=cuda_device) * 0.7).to(torch.bfloat16)
+    want = torch.zeros(256, dtype=torch.int64, device=cuda_device)
+    for b in range(B):
+        e = (x[b].view(torch.int16).to(torch.int32) >> 7) & 0xFF
+        want += torch.bincount(e.flatten(), minlength=256)
+    chunk, hist = codec.pack_blocks(x, 127, 3, 128, need_hist=True)
+    assert torch.equal(hist.to(torch.int64), want)
+    assert chunk.n_escapes == int(want.sum() - want[121:128].sum())
+    out = torch.empty_like(x)
+    codec.unpack_chunk(chunk, out)
+    assert torch.equal(out.view(torch.int16), x.view(torch.int16))
+    codec.check_device_status(cuda_device)
