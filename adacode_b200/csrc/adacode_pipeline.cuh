@@ -748,6 +748,7 @@ struct alignas(128) PackSmemT {
     int hist[256];
     int is_last;
     long long carry;
+    long long job_off[kMaxJobs];
     int scan[G::kWarps];
 };
 static_assert(sizeof(PackStageT<WideGeom>) % 128 == 0 && sizeof(PackStageT<NarrowGeom>) % 128 == 0,
@@ -790,26 +791,47 @@ __device__ __forceinline__ int job_of_tile(const PackPipeArgs &pa, int64_t tile)
 
 // Turn per-tile escape counts into per-segment inclusive tile bases and segment offsets (per job).
 // Run by the consumer threads of the CTA that finished last, while the rest of the GPU is idle,
-// so it is kept short: every thread takes a run of kScanRun consecutive tiles, fetches their
-// counts with independent loads (one memory round trip per pass of threads x kScanRun tiles), and
-// one block scan of the run totals gives every tile its prefix.
+// so it is kept short: every thread takes a run of kScanRun consecutive tiles; the counts of the
+// next pass (threads x kScanRun tiles) are fetched while the current pass is worked on, so the
+// memory round trip of a pass is hidden; one block scan of the run totals gives every tile its
+// prefix; and the escape offsets of the blocks that begin inside the pass travel through shared
+// memory (`boff`, one entry per block touched by the pass, in the idle staging buffers), not
+// through global memory.
 constexpr int kScanRun = 8;
 
 template <class G>
-__device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long long *s_carry, int *s_scan) {
+__device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long long *s_carry, int *s_scan,
+                                                 long long *s_job_off, long long *boff_raw) {
+    // All offsets of a launch fit 32 bits (it has fewer than 2**31 elements), and a thread walks
+    // consecutive tiles, so block index, position in the block and job advance by comparison:
+    // one division per thread and pass.  (One SM does all of this while the others wait.)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per_pass = G::kConsumers * kScanRun;
+    const int n_tiles = (int)pa.n_tiles, BH = pa.BH;
+    int *carry = reinterpret_cast<int *>(s_carry);
+    int *job_off = reinterpret_cast<int *>(s_job_off);
+    int *boff = reinterpret_cast<int *>(boff_raw);
     if (tid == 0) {
-        *s_carry = 0;
+        *carry = 0;
         pa.blk_off[0] = 0;
+        boff[0] = 0;
     }
+    if (tid < kMaxJobs) job_off[tid] = 0;
     if (tid < pa.n_jobs) pa.job[tid].seg_off[0] = 0;
-    consumer_sync<G::kConsumers>();
-    const int64_t per_pass = (int64_t)G::kConsumers * kScanRun;
-    for (int64_t pass = 0; pass < pa.n_tiles; pass += per_pass) {
-        const int64_t t0 = pass + (int64_t)tid * kScanRun;
-        int c[kScanRun];
+    int c[kScanRun], nxt[kScanRun];
 #pragma unroll
-        for (int i = 0; i < kScanRun; ++i) c[i] = (t0 + i < pa.n_tiles) ? __ldcg(pa.tile_counts + t0 + i) : 0;
+    for (int i = 0; i < kScanRun; ++i) {
+        const int t = tid * kScanRun + i;
+        c[i] = t < n_tiles ? __ldcg(pa.tile_counts + t) : 0;
+    }
+    consumer_sync<G::kConsumers>();
+    for (int pass = 0; pass < n_tiles; pass += per_pass) {
+        const int t0 = pass + tid * kScanRun;
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) {
+            const int t = t0 + per_pass + i;
+            nxt[i] = t < n_tiles ? __ldcg(pa.tile_counts + t) : 0;
+        }
         int run = 0;
 #pragma unroll
         for (int i = 0; i < kScanRun; ++i) run += c[i];
@@ -828,28 +850,65 @@ __device__ __forceinline__ void scan_tile_counts(const PackPipeArgs &pa, long lo
             wp += (i < warp) ? v : 0;
             tot += v;
         }
-        long long incl = *s_carry + wp + (x - run);       // escapes before this thread's run
-        long long inc[kScanRun];
+        const int gb0 = pass / BH;                        // the block the pass begins in; boff[0] is its offset
+        const int gb_first = t0 / BH, rem_first = t0 - gb_first * BH;
+        int incl = *carry + wp + (x - run);               // escapes before this thread's run
+        int inc[kScanRun];
+        {
+            int gb = gb_first, rem = rem_first;
 #pragma unroll
-        for (int i = 0; i < kScanRun; ++i) {
-            const int64_t t = t0 + i;
-            incl += c[i];
-            inc[i] = incl;                                // inclusive prefix over the whole launch
-            if (t < pa.n_tiles && (t + 1) % pa.BH == 0) pa.blk_off[(t + 1) / pa.BH] = incl;
-        }
-        consumer_sync<G::kConsumers>();                                  // block offsets up to the end of this pass are written
-        if (tid == 0) *s_carry += tot;
-#pragma unroll
-        for (int i = 0; i < kScanRun; ++i) {
-            const int64_t t = t0 + i;
-            if (t < pa.n_tiles) {
-                const int64_t gb = t / pa.BH;
-                const PackJob &jb = pa.job[job_of_tile(pa, t)];
-                jb.tile_base[t - jb.tile0] = (int32_t)(inc[i] - pa.blk_off[gb]);
-                if ((t + 1) % pa.BH == 0) jb.seg_off[gb + 1 - jb.blk0] = inc[i] - pa.blk_off[jb.blk0];
+            for (int i = 0; i < kScanRun; ++i) {
+                incl += c[i];
+                inc[i] = incl;                            // inclusive prefix over the whole launch
+                if (++rem == BH) {                        // tile t0 + i ends block gb
+                    rem = 0;
+                    ++gb;
+                    if (t0 + i < n_tiles) {
+                        pa.blk_off[gb] = incl;
+                        boff[gb - gb0] = incl;
+                        for (int j = 1; j < pa.n_jobs; ++j)
+                            if (pa.job[j].blk0 == gb) job_off[j] = incl;
+                    }
+                }
             }
         }
+        consumer_sync<G::kConsumers>();                   // the offsets of the blocks of this pass are in boff
+        if (t0 < n_tiles) {
+            int gb = gb_first, rem = rem_first;
+            int j = job_of_tile(pa, t0);
+            int j_end = j + 1 < pa.n_jobs ? (int)pa.job[j + 1].tile0 : n_tiles;
+            int32_t *tb = pa.job[j].tile_base - pa.job[j].tile0;
+            int start = boff[gb - gb0];                   // offset at which block gb begins
+#pragma unroll
+            for (int i = 0; i < kScanRun; ++i) {
+                const int t = t0 + i;
+                if (t < n_tiles) {
+                    if (t == j_end) {
+                        ++j;
+                        j_end = j + 1 < pa.n_jobs ? (int)pa.job[j + 1].tile0 : n_tiles;
+                        tb = pa.job[j].tile_base - pa.job[j].tile0;
+                    }
+                    tb[t] = inc[i] - start;
+                    if (++rem == BH) {
+                        rem = 0;
+                        ++gb;
+                        pa.job[j].seg_off[gb - pa.job[j].blk0] = (long long)(inc[i] - job_off[j]);
+                        start = inc[i];                   // = boff[gb - gb0]
+                    }
+                }
+            }
+        }
+        // the block the next pass begins in may have begun in this one
+        const int gb1 = (pass + per_pass) / BH;
+        const int carry_off = boff[gb1 - gb0];
         consumer_sync<G::kConsumers>();
+        if (tid == 0) {
+            *carry += tot;
+            boff[0] = carry_off;
+        }
+#pragma unroll
+        for (int i = 0; i < kScanRun; ++i) c[i] = nxt[i];
+        // (no barrier here: what thread 0 just wrote is read after the next pass's first barrier)
     }
     if (tid == 0) *pa.done = 0u;
 }
@@ -1141,7 +1200,8 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
     consumer_sync<G::kConsumers>();
     if (!s.is_last) return;
     __threadfence();
-    scan_tile_counts<G>(pa, &s.carry, s.scan);
+    // (the staging buffers are idle by now: every unit of this CTA has been consumed and stored)
+    scan_tile_counts<G>(pa, &s.carry, s.scan, s.job_off, reinterpret_cast<long long *>(&s.stage[0]));
 }
 
 // One warp copies the escape bytes of tile t (its units follow each other in the scratch) to `dst`
