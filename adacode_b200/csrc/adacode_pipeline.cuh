@@ -520,7 +520,9 @@ template <class G>
 __device__ __forceinline__ bool wait_loaded(UnpackSmemT<G> &s, uint32_t it, int32_t *status, uint32_t poll_limit) {
     bool loaded = true;
     if ((threadIdx.x & 31) == 0) loaded = mbar_wait(&s.full[it % kStages], (it / kStages) & 1, status, poll_limit);
-    return __shfl_sync(kFull, loaded, 0);
+    loaded = __shfl_sync(kFull, loaded, 0);
+    __syncwarp();          // orders the other lanes' reads of the stage after lane 0's wait
+    return loaded;
 }
 
 // Units it, it + 1, ... as long as they carry code length N and window `left` (the decode table
@@ -1145,7 +1147,9 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
     auto wait_loaded = [&](uint32_t u) {
         bool loaded = true;
         if (lane == 0) loaded = mbar_wait(&s.full[u % kStages], (u / kStages) & 1, pa.status, pa.poll_limit);
-        return (bool)__shfl_sync(kFull, loaded, 0);
+        loaded = __shfl_sync(kFull, loaded, 0);
+        __syncwarp();      // orders the other lanes' reads of the stage after lane 0's wait
+        return loaded;
     };
     uint32_t it = 0;
     while (it < my_units) {
