@@ -821,8 +821,14 @@ def e2e_leg(args, dev, world: int, rank: int, slots, calib, per: int, b0: int, r
     cfg = StubConfig(n_l)
     rights = [(calib[(l, 'k')][0], calib[(l, 'v')][0]) for l in range(n_l)]
     nbits = [(calib[(l, 'k')][1], calib[(l, 'v')][1]) for l in range(n_l)]
-    host_in = [[x.to('cpu').pin_memory() for x in slots[l]['x']] for l in range(n_l)]
-    host_out = [torch.empty_like(host_in[0][0]).pin_memory() for _ in range(2)]
+    def pinned_copy(x):
+        # straight into pinned memory: no pageable copy in between (eight ranks pin about 80 GB of one host)
+        h = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+        h.copy_(x)
+        return h
+
+    host_in = [[pinned_copy(x) for x in slots[l]['x']] for l in range(n_l)]
+    host_out = [torch.empty(host_in[0][0].shape, dtype=torch.bfloat16, pin_memory=True) for _ in range(2)]
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     shape = tuple(slots[0]['x'][0].shape)
     release_workload()
