@@ -684,14 +684,27 @@ int ensure_dynamic_smem(Kernel kernel, size_t bytes) {
 uint32_t g_poll_limit = kMaxPolls;
 int g_withhold_unit = -1;
 
+// Launch as a programmatic dependent of whatever precedes it in the stream: the kernel may be set up
+// (barriers, tables in shared memory) while its predecessor's last CTAs still run; it executes
+// griddepcontrol.wait before it touches global memory.
+template <typename Kernel, typename Args>
+int launch_dependent(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, const Args &args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = dim3(threads), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    ADACODE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, args));
+    return ADACODE_OK;
+}
+
 template <class G>
 int launch_unpack_geom(const UnpackJobsArgs &ja, cudaStream_t st) {
     int rc = ensure_dynamic_smem(k_unpack_pipe<G>, sizeof(UnpackSmemT<G>));
     if (rc != ADACODE_OK) return rc;
     const int grid = grid_for(ja.tile0[ja.n_jobs], G::kCtasPerSm);
-    k_unpack_pipe<G><<<grid, G::kThreads, sizeof(UnpackSmemT<G>), st>>>(ja);
-    ADACODE_CUDA_TRY(cudaGetLastError());
-    return ADACODE_OK;
+    return launch_dependent(k_unpack_pipe<G>, dim3(grid), G::kThreads, sizeof(UnpackSmemT<G>), st, ja);
 }
 
 // ADACODE_UNPACK_GEOMETRY=wide keeps the unpack kernel on the 16-warp geometry (for comparisons)
@@ -724,9 +737,7 @@ template <class G, typename Kernel>
 int launch_pack_kernel(Kernel kernel, const PackPipeArgs &pa, cudaStream_t st) {
     int rc = ensure_dynamic_smem(kernel, sizeof(PackSmemT<G>));
     if (rc != ADACODE_OK) return rc;
-    kernel<<<grid_for(pa.n_tiles, G::kCtasPerSm), G::kThreads, sizeof(PackSmemT<G>), st>>>(pa);
-    ADACODE_CUDA_TRY(cudaGetLastError());
-    return ADACODE_OK;
+    return launch_dependent(kernel, dim3(grid_for(pa.n_tiles, G::kCtasPerSm)), G::kThreads, sizeof(PackSmemT<G>), st, pa);
 }
 
 template <int N, class G>
@@ -778,10 +789,10 @@ int launch_pack_pipe(PackPipeArgs &pa, int nbits, cudaStream_t st) {
     const int64_t want = (job_tiles + kWarps - 1) / kWarps;
     const int64_t cap = ((int64_t)sm_count() * 4 + pa.n_jobs - 1) / pa.n_jobs;
     const dim3 cgrid((unsigned)(want < cap ? want : cap), (unsigned)pa.n_jobs);
-    if (hist) k_compact_units<true><<<cgrid, kThreads, 0, st>>>(pa);
-    else k_compact_units<false><<<cgrid, kThreads, 0, st>>>(pa);
-    ADACODE_CUDA_TRY(cudaGetLastError());
-    return ADACODE_OK;
+    // (a programmatic dependent of the pack kernel: it is set up, and clears its histogram copies, while
+    // the pack kernel's last CTAs still run)
+    return hist ? launch_dependent(k_compact_units<true>, cgrid, kThreads, 0, st, pa)
+                : launch_dependent(k_compact_units<false>, cgrid, kThreads, 0, st, pa);
 }
 
 template <int N, int CH>

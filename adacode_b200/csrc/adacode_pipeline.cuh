@@ -573,6 +573,8 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
         m.elems = 0, m.left = 0, m.nbits = 1, m.first_unit_of_tile = 1, m.ds = 0;
     }
     __syncthreads();
+    // launched as a programmatic dependent of its predecessor in the stream: no global memory is touched above
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int unit_rows = unit_rows_for<G::kUnit>(a0.seq_tile, a0.D);
     const int units_per_tile = (a0.seq_tile + unit_rows - 1) / unit_rows;
@@ -650,6 +652,7 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_unpack_pipe(cons
         }
     }
     bulk_wait_all();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 #ifndef ADACODE_PIPELINE_UNPACK_ONLY
@@ -1075,6 +1078,8 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
         m.elems = 0, m.first_unit_of_tile = 1, m.last_unit_of_tile = 0, m.job = 0;
     }
     __syncthreads();
+    // launched as a programmatic dependent of its predecessor in the stream: no global memory is touched above
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int unit_rows = pa.unit_rows, upt = pa.units_per_tile;
 
@@ -1195,6 +1200,8 @@ __global__ void __launch_bounds__(G::kThreads, G::kCtasPerSm) k_pack_pipe(const 
         }
     }
     bulk_wait_all();
+    // the compaction pass may be set up from here on (it waits for this launch to complete before it reads)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __threadfence();
     consumer_sync<G::kConsumers>();
     if (tid == 0) {
@@ -1286,6 +1293,8 @@ __global__ void __launch_bounds__(kThreads) k_compact_units(const __grid_constan
         for (int i = tid; i < kWarps * 4 * 256; i += kThreads) (&s_hist[0][0][0])[i] = 0;
         __syncthreads();
     }
+    // launched as a programmatic dependent of the pack kernel: nothing that kernel wrote is read above
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     int *my_hist = &s_hist[HIST ? warp : 0][HIST ? (lane & 3) : 0][0];
     const int64_t warp_global = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t n_warps = (int64_t)gridDim.x * kWarps;
