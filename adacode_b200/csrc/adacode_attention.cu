@@ -297,6 +297,8 @@ __global__ void k_decode_attn_combine(const float *__restrict__ part_o, const fl
     const int hkv = hq / G, g = hq - hkv * G;
     const int d = threadIdx.x;
     if (d >= D) return;
+    // launched as a programmatic dependent of the attention kernel: wait for its partial results
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const long long base = ((long long)b * Hkv + hkv) * n_splits;
     float mx = -INFINITY;
     for (int sidx = 0; sidx < n_splits; ++sidx) mx = fmaxf(mx, part_ml[((base + sidx) * G + g) * 2]);
@@ -593,6 +595,8 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_decode_attn_pipe(const Attn
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // launched as a programmatic dependent of its predecessor in the stream: no global memory is touched above
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // queries (zero rows beyond G), running statistics
     for (int i = tid; i < kMaxGroup * kQPad; i += kPipeThreads) {
         const int g = i / kQPad, d = i - g * kQPad;
@@ -730,6 +734,22 @@ int pick_splits(int B, int Hkv, int items, int D) {
 
 }  // namespace
 
+namespace {
+// Programmatic dependent launch: the kernel may be set up while its predecessor in the stream drains;
+// it executes griddepcontrol.wait before it reads or writes global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_as_dependent(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t st,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = dim3(threads), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+}  // namespace
+
 extern "C" {
 
 size_t adacode_decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits) {
@@ -797,13 +817,16 @@ int adacode_decode_attn(const void *q_bf16, int64_t q_stride_b, int64_t q_stride
         u.dst = nullptr, u.db = 0, u.dh = 0, u.ds = 0, u.status = status;
         pa.k = u, pa.v = u;
         pa.k.seg = k_segments_dev, pa.v.seg = v_segments_dev;
-        k_decode_attn_pipe<<<dim3(B * Hkv, n_splits, head_groups), kPipeThreads, sizeof(AttnPipeSmem), st>>>(pa);
+        if (launch_as_dependent(k_decode_attn_pipe, dim3(B * Hkv, n_splits, head_groups), kPipeThreads,
+                                sizeof(AttnPipeSmem), st, pa) != cudaSuccess)
+            return ADACODE_ERR_CUDA;
     } else {
         k_decode_attn<<<dim3(B * Hkv, n_splits, head_groups), kAttnThreads, sizeof(AttnSmem), st>>>(a);
     }
     if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;
-    k_decode_attn_combine<<<B * Hq, D, 0, st>>>(a.part_o, a.part_ml, Hq, Hkv, G, D, n_splits, (uint16_t *)out_bf16);
-    if (cudaGetLastError() != cudaSuccess) return ADACODE_ERR_CUDA;
+    if (launch_as_dependent(k_decode_attn_combine, dim3(B * Hq), D, 0, st, (const float *)a.part_o,
+                            (const float *)a.part_ml, Hq, Hkv, G, D, n_splits, (uint16_t *)out_bf16) != cudaSuccess)
+        return ADACODE_ERR_CUDA;
     return ADACODE_OK;
 }
 
